@@ -53,8 +53,12 @@ class CacheGroup:
         self.storage = None
         self.table = None
         if allocate:
-            self.storage = torch.zeros(cache_layers, num_pages, 2, request.num_kv_heads, page_size,
-                                       request.head_dim, dtype=dtype, device=device)
+            if request.value_dim == request.head_dim:
+                self.storage = torch.zeros(cache_layers, num_pages, 2, request.num_kv_heads, page_size,
+                                           request.head_dim, dtype=dtype, device=device)
+            else:       # per page the keys [kv head][slot][head_dim], then the values [kv head][slot][v_head_dim]
+                self.storage = torch.zeros(cache_layers, num_pages, page_size * request.elems_per_token,
+                                           dtype=dtype, device=device)
             self.table = torch.zeros(max_rows, max_pages_per_seq, dtype=torch.int32, device=device)
 
     @property
@@ -63,7 +67,7 @@ class CacheGroup:
 
     def bytes_per_page(self, itemsize: int) -> int:
         r = self.request
-        return self.cache_layers * 2 * r.num_kv_heads * self.page_size * r.head_dim * itemsize
+        return self.cache_layers * self.page_size * r.elems_per_token * itemsize
 
 
 class CacheManager:

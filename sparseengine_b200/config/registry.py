@@ -38,6 +38,8 @@ def architectures() -> list[str]:
 
 def resolve_architecture(config: dict) -> Architecture:
     names = config.get("architectures") or []
+    if not names and isinstance(config.get("architecture"), str):      # some families name it in the singular
+        names = [config["architecture"]]
     if not isinstance(names, (list, tuple)) or len(names) != 1:
         raise ValueError(f"config.json must name exactly one architecture, got {names!r}")
     name = names[0]
@@ -55,9 +57,33 @@ def read_config_json(model_dir: str) -> dict:
         return json.load(f)
 
 
+def checkpoint_shapes(model_dir: str) -> dict:
+    """Name -> shape of every tensor in the folder's ``*.safetensors`` files, from their headers
+    alone (8 bytes of length, then that much JSON)."""
+    import glob
+    import struct
+    out = {}
+    for path in sorted(glob.glob(os.path.join(model_dir, "*.safetensors"))):
+        with open(path, "rb") as f:
+            (n,) = struct.unpack("<Q", f.read(8))
+            header = json.loads(f.read(n))
+        for name, rec in header.items():
+            if name != "__metadata__":
+                out[name] = tuple(rec["shape"])
+    return out
+
+
 def load_model_spec(model_dir_or_dict) -> tuple[Any, ModelSpec]:
-    """Return ``(typed config, ModelSpec)`` for a model folder or a config dictionary."""
-    raw = model_dir_or_dict if isinstance(model_dir_or_dict, dict) else read_config_json(model_dir_or_dict)
+    """Return ``(typed config, ModelSpec)`` for a model folder or a config dictionary.
+
+    An architecture whose configuration leaves a size to the checkpoint (a low rank that only a
+    tensor's shape gives) sets ``uses_checkpoint_shapes`` on its configuration class; its
+    ``from_dict`` then also gets the shapes of a folder's tensors (``None`` for a dictionary)."""
+    is_dict = isinstance(model_dir_or_dict, dict)
+    raw = model_dir_or_dict if is_dict else read_config_json(model_dir_or_dict)
     arch = resolve_architecture(raw)
-    typed = arch.config_class.from_dict(raw)
+    if getattr(arch.config_class, "uses_checkpoint_shapes", False):
+        typed = arch.config_class.from_dict(raw, None if is_dict else checkpoint_shapes(model_dir_or_dict))
+    else:
+        typed = arch.config_class.from_dict(raw)
     return typed, arch.build(typed)

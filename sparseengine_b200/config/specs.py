@@ -67,6 +67,15 @@ class RMSNormSpec:
 
 
 @dataclass(frozen=True)
+class LayerNormSpec:
+    """Layer norm with a weight and (``bias``) a bias: (x - mean) / sqrt(var + eps) * w + b."""
+    kind: str = "layer_norm"
+    size: int = 0
+    eps: float = 1e-6
+    bias: bool = True
+
+
+@dataclass(frozen=True)
 class AttentionSpec:
     """Grouped-query attention over a paged key/value cache."""
     kind: str = "attention"
@@ -79,6 +88,51 @@ class AttentionSpec:
     qk_norm_eps: float = 1e-6
     window: Optional[int] = None      # keys p-window+1..p; None = all keys
     position: Optional[Any] = None    # a position-encoding spec (e.g. RotarySpec)
+    # "rotary": the fused norm + rotation kernel (values as wide as keys).  "general": no rotation;
+    # the fields below apply, and norms and temperature are computed in 32-bit and rounded once.
+    prep: str = "rotary"
+    v_head_dim: Optional[int] = None  # the values' head size (None: head_dim)
+    # (coef, every): the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1)
+    q_temperature: Optional[tuple] = None
+    own_kv: bool = True               # False: no key/value projections; the layer attends over another's cache
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
+
+
+@dataclass(frozen=True)
+class StateSpaceSpec:
+    """Selective state-space mixer (state-space duality form): per head a state of
+    ``state_size x head_dim`` with a scalar decay, inputs through a short causal convolution,
+    output gated and RMS-normed in ``norm_groups`` equal parts."""
+    kind: str = "mamba2"
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    state_size: int = 0
+    groups: int = 1                   # heads of one group share B and C
+    conv_taps: int = 4
+    norm_groups: int = 1
+    norm_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """Gated delta rule with one decay per head and key channel: per head a state of
+    ``head_dim x v_head_dim``; q, k, v through short causal convolutions; the decay and the output
+    gate come through low-rank projections of the given ranks."""
+    kind: str = "channel_delta"
+    hidden_size: int = 0
+    num_heads: int = 0
+    num_kv_heads: int = 0             # q/k heads; value head h uses q/k head h // (num_heads / num_kv_heads)
+    head_dim: int = 0
+    v_head_dim: int = 0
+    conv_taps: int = 4
+    decay_rank: int = 0
+    gate_rank: int = 0
+    norm_eps: float = 1e-6
+    unit_eps: float = 1e-6            # q and k become x / sqrt(sum(x^2) + unit_eps)
 
 
 @dataclass(frozen=True)
@@ -106,6 +160,15 @@ class DenseMLPSpec:
 
 
 @dataclass(frozen=True)
+class PlainMLPSpec:
+    """An ungated feed-forward: down(act(up(x)))."""
+    kind: str = "plain_mlp"
+    hidden_size: int = 0
+    intermediate_size: int = 0
+    activation: str = "relu2"         # "relu2" (squared relu) | "gelu_tanh" | "silu" | "relu"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One layer: its parts and the name of their arrangement in a block.
 
@@ -119,6 +182,9 @@ class LayerSpec:
     mixer_norm: Any
     feed_forward_norm: Any
     arrangement: str = "pre_norm"
+    # "post_norm": x <- norm(residual_scale * x + sublayer(x)) for each sublayer; the feed-forward
+    # (with its norm) may be None
+    residual_scale: float = 1.0
     extra: dict = field(default_factory=dict)       # part name -> spec, for arrangements with more parts
     # part-local parameter name -> tuple[Source, ...]; keys are "<part>.<param>" with
     # part in {"mixer", "feed_forward", "mixer_norm", "feed_forward_norm"}.
@@ -149,6 +215,7 @@ class ModelSpec:
     order: Sequence[ScheduleEntry]
     final_norm: Any
     final_norm_source: str = "model.norm.weight"
+    final_norm_sources: Optional[dict] = None       # parameter name -> checkpoint name, for a final norm with several
     embed_source: str = "model.embed_tokens.weight"
     head_source: Optional[str] = "lm_head.weight"   # None = tied to the embedding
     embed_scale: float = 1.0                        # the embedded tokens are multiplied by this (in the activation type)
@@ -156,3 +223,7 @@ class ModelSpec:
     ignored_prefixes: tuple = ()                    # checkpoint names skipped at load
     ignored_rule: Optional[Any] = None              # name -> bool: further names skipped at load
     stored_dtype: str = "bfloat16"
+    # "activation": blocks carry (hidden, residual) in the activation type.  "float32": the residual
+    # stream is 32-bit whatever the activation type; blocks carry (its copy in the activation type,
+    # the stream), the embedding is scaled in 32-bit and the final norm reads the stream.
+    residual_stream: str = "activation"

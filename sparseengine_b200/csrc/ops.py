@@ -26,7 +26,7 @@ _fns: dict = {}
 
 # Kernels launched through these bindings since the process started (a launcher that
 # starts two kernels counts two).  Benchmarks read the difference around a timed region.
-KERNELS_PER_CALL = {"se_attn_decode": 2, "se_router": 2}   # upper bounds per call
+KERNELS_PER_CALL = {"se_attn_decode": 2, "se_router": 2, "se_causal_conv": 2}   # upper bounds per call
 launch_count = 0
 calls: dict = {}     # launcher name -> times called (tests check which kernels a path took)
 
@@ -45,6 +45,8 @@ LIMITS = {
     "router_max_unaligned_width": 6400,     # widths that are no multiple of 4 keep 8 token rows in shared memory
     "moe_max_experts": 6079,                # the routing build's scans keep two ints per expert in shared memory
     "attention_max_head_dim": 256,          # in steps of 16
+    "layernorm_max_width": 51200,           # as the RMS norm: the row is kept in shared memory in 32-bit
+    "recurrent_max_state_rows": 512,        # rows of a recurrence's state on the key/state side (16 registers x 32 lanes)
     "grid_dim_yz": 65535,                   # heads, KV heads and a step's entries map to grid dimensions y and z
 }
 
@@ -181,16 +183,135 @@ def qk_prep(qkv, q_w, k_w, inv_freq, positions, token_seq, seq_rows, table, cach
 
 
 def paged_attention_plain(q, cache, table, seq_rows, token_seq, positions, out, *, num_heads, num_kv_heads,
-                          head_dim, page_size, scale, window=None, num_pages=None):
+                          head_dim, page_size, scale, window=None, num_pages=None, v_head_dim=None):
+    """``v_head_dim``: the values' head size where it differs from the queries' and keys'."""
     tokens = q.shape[0]
     dt = q.dtype
-    _check(_fn("se_paged_attention_plain", "pppipppp" "iiiii" "f" "iip" "ip")(
+    _check(_fn("se_paged_attention_plain", "pppipppp" "iiiiii" "f" "iip" "ip")(
         _ptr(q, None, "q"), _ptr(cache, dt, "cache"), _ptr(table, torch.int32, "table"), table.shape[1],
         _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(token_seq, torch.int32, "token_seq"),
         _ptr(positions, torch.int32, "positions"), _ptr(out, dt, "out"), tokens, num_heads, num_kv_heads,
-        head_dim, page_size, float(scale), int(window or 0),
+        head_dim, int(v_head_dim or head_dim), page_size, float(scale), int(window or 0),
         cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)),
         dtype_code(dt), _stream()), "paged_attention_plain")
+    return out
+
+
+def qk_prep_general(proj, q_w, k_w, positions, token_seq, seq_rows, table, cache, q_out, *, num_heads, num_kv_heads,
+                    head_dim, v_head_dim, eps, page_size, has_kv=True, temperature=None, num_pages=None):
+    """Query/key preparation without rotation: whole-projection RMS norms (optional), a query
+    temperature ``(coef, every)`` (q times 1 + coef ln(floor((p+1)/every) + 1)), keys and values of
+    different head sizes into their page; ``has_kv=False``: the row holds queries only."""
+    tokens = proj.shape[0]
+    dt = proj.dtype
+    if proj.dim() != 2 or proj.stride(1) != 1:
+        raise ValueError("proj must be a matrix with contiguous rows")
+    coef, every = (float(temperature[0]), int(temperature[1])) if temperature else (0.0, 0)
+    _check(_fn("se_qk_prep_general", "pipp" "ppp" "pi" "pp" "iiiii" "f" "fi" "iiip" "ip")(
+        proj.data_ptr(), proj.stride(0), _ptr(q_w, dt, "q_norm"), _ptr(k_w, dt, "k_norm"),
+        _ptr(positions, torch.int32, "positions"), _ptr(token_seq, torch.int32, "token_seq"),
+        _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(table, torch.int32, "table"), table.shape[1] if table is not None else 0,
+        _ptr(cache, dt, "cache") if has_kv else None, _ptr(q_out, dt, "q_out"), tokens, num_heads, num_kv_heads, head_dim,
+        int(v_head_dim), float(eps), coef, every, page_size, int(bool(has_kv)),
+        (cache.shape[0] if num_pages is None else int(num_pages)) if has_kv else 0, _ptr(error_word(proj.device)),
+        dtype_code(dt), _stream()), "qk_prep_general")
+    return q_out
+
+
+# ---- a 32-bit residual stream (csrc/stream32.cu) -------------------------------------------------
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def embed_stream(table, ids, stream, act=None, scale: float = 1.0):
+    """stream[t] = table[ids[t]] * scale in 32-bit; ``act``: the same rounded to the table's type."""
+    tokens, hidden = stream.shape
+    _check(_fn("se_embed_stream", "pppp" "iii" "f" "ip")(
+        _ptr(table, None, "table"), _ptr(ids, torch.int32, "ids"), _ptr(stream, torch.float32, "stream"),
+        _ptr(act, table.dtype, "act"), tokens, hidden, table.shape[0], float(scale), dtype_code(table.dtype), _stream()),
+        "embed_stream")
+    return stream
+
+
+def add_layernorm(x, y, alpha: float, w, b, eps: float, out32=None, out_act=None):
+    """Layer norm (weight ``w``, optional bias ``b``) of ``alpha * x + y``: ``x`` is the 32-bit
+    stream, ``y`` (optional) has the weights' type; ``out32`` receives the result in 32-bit,
+    ``out_act`` in the weights' type."""
+    rows, hidden = x.shape
+    dt = w.dtype
+    if w.shape != (hidden,):
+        raise ValueError(f"norm weight shape {tuple(w.shape)} does not match width {hidden}")
+    _check(_fn("se_add_layernorm", "pp" "f" "pppp" "ii" "f" "ip")(
+        _ptr(x, torch.float32, "x"), _ptr(y, dt, "y"), float(alpha), _ptr(w), _ptr(b, dt, "b"),
+        _ptr(out32, torch.float32, "out32"), _ptr(out_act, dt, "out_act"), rows, hidden, float(eps), dtype_code(dt),
+        _stream()), "add_layernorm")
+
+
+def activation_(x, kind: str):
+    """An activation of :data:`ACTIVATIONS` in place (32-bit arithmetic, rounded once)."""
+    if kind not in ACTIVATIONS:
+        raise ValueError(f"activation {kind!r} is not known; known: {sorted(ACTIVATIONS)}")
+    _check(_fn("se_activation", "plii" "p")(_ptr(x, None, "x"), x.numel(), ACTIVATIONS[kind], dtype_code(x.dtype),
+                                           _stream()), "activation")
+    return x
+
+
+# ---- mixers with a recurrent state (csrc/recurrent.cu) -------------------------------------------
+
+def causal_conv(x, c0: int, w, bias, state, conv_off: int, step, out):
+    """out[t, c] = silu(bias[c] + sum_j w[c, j] x[t - (taps-1-j), c0 + c]) over each request's own
+    tokens; what lies before this step's tokens comes from the carried inputs in ``state`` (rows
+    ``step.state_rows``, from element ``conv_off`` on, ``[taps-1, C]``), which are brought up to date."""
+    tokens = x.shape[0]
+    C, taps = w.shape
+    _check(_fn("se_causal_conv", "pii" "pp" "pli" "ppp" "p" "iiii" "ip")(
+        x.data_ptr(), x.stride(0), int(c0), _ptr(w, torch.float32, "conv weight"), _ptr(bias, torch.float32, "conv bias"),
+        _ptr(state, torch.float32, "state"), state.stride(0), int(conv_off), _ptr(step.token_seq), _ptr(step.cu_q),
+        _ptr(step.seq_rows), _ptr(out, torch.float32, "out"), tokens, step.num_seqs, C, taps, dtype_code(x.dtype),
+        _stream()), "causal_conv")
+    return out
+
+
+def ssm_scan(xbc, proj, dt_off: int, dt_bias, a_log, d_skip, state, step, y, *, heads, head_dim, state_size, groups):
+    _check(_fn("se_ssm_scan", "ppii" "ppp" "pl" "pp" "p" "iiiii" "ip")(
+        _ptr(xbc, torch.float32, "xbc"), proj.data_ptr(), proj.stride(0), int(dt_off), _ptr(dt_bias, torch.float32),
+        _ptr(a_log, torch.float32), _ptr(d_skip, torch.float32), _ptr(state, torch.float32, "state"), state.stride(0),
+        _ptr(step.cu_q), _ptr(step.seq_rows), _ptr(y, torch.float32, "y"), step.num_seqs, heads, head_dim, state_size,
+        groups, dtype_code(proj.dtype), _stream()), "ssm_scan")
+    return y
+
+
+def gated_group_norm(y, proj, z_off: int, w, out, *, parts: int, eps: float):
+    tokens, inner = y.shape
+    _check(_fn("se_gated_group_norm", "ppii" "pp" "iii" "f" "ip")(
+        _ptr(y, torch.float32, "y"), proj.data_ptr(), proj.stride(0), int(z_off), _ptr(w, torch.float32, "w"),
+        _ptr(out, proj.dtype, "out"), tokens, inner, parts, float(eps), dtype_code(proj.dtype), _stream()),
+        "gated_group_norm")
+    return out
+
+
+def delta_prep(qkv, a, proj, b_off: int, dt_bias, a_log, dec, beta, *, heads, kv_heads, head_dim, v_head_dim,
+               unit_eps: float, q_scale: float):
+    _check(_fn("se_delta_prep", "pppii" "pp" "pp" "iiiii" "ff" "ip")(
+        _ptr(qkv, torch.float32, "qkv"), _ptr(a, proj.dtype, "a"), proj.data_ptr(), proj.stride(0), int(b_off),
+        _ptr(dt_bias, torch.float32), _ptr(a_log, torch.float32), _ptr(dec, torch.float32), _ptr(beta, torch.float32),
+        qkv.shape[0], heads, kv_heads, head_dim, v_head_dim, float(unit_eps), float(q_scale), dtype_code(proj.dtype),
+        _stream()), "delta_prep")
+
+
+def delta_scan(qkv, dec, beta, state, step, o, *, heads, kv_heads, head_dim, v_head_dim):
+    _check(_fn("se_delta_scan", "ppp" "pl" "pp" "p" "iiiii" "p")(
+        _ptr(qkv, torch.float32, "qkv"), _ptr(dec, torch.float32), _ptr(beta, torch.float32),
+        _ptr(state, torch.float32, "state"), state.stride(0), _ptr(step.cu_q), _ptr(step.seq_rows),
+        _ptr(o, torch.float32, "o"), step.num_seqs, heads, kv_heads, head_dim, v_head_dim, _stream()), "delta_scan")
+    return o
+
+
+def delta_out(o, gate, w, out, *, v_head_dim: int, eps: float):
+    rows = o.numel() // v_head_dim
+    _check(_fn("se_delta_out", "pppp" "ii" "f" "ip")(
+        _ptr(o, torch.float32, "o"), _ptr(gate, out.dtype, "gate"), _ptr(w, torch.float32, "w"), _ptr(out), rows,
+        v_head_dim, float(eps), dtype_code(out.dtype), _stream()), "delta_out")
     return out
 
 

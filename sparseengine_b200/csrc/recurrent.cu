@@ -1,0 +1,400 @@
+// Mixers with a recurrent state of fixed size per request: a short causal convolution over
+// time with carried inputs, the selective state-space recurrence (scalar decay per head, state
+// N x P) and the gated delta rule (one decay per head and key channel, state d x dv), with
+// their prologues and epilogues.  Everything that enters a recurrence is 32-bit.
+//
+// A step's batch is ragged: entry e owns tokens cu_q[e] .. cu_q[e+1]-1 (consecutive positions of
+// one request) and state row seq_rows[e]; token t belongs to entry token_seq[t].  Everything
+// that changes from step to step is read from these device arrays, so the launches can be
+// replayed from a CUDA graph.  A request's state row starts as zeros.
+//
+// State row of a mixer (32-bit floats): the recurrence's matrix per head, stored [head][column
+// of the value side][row of the key/state side], followed by the convolution's last taps-1
+// inputs [taps-1][channel].
+#include "common.cuh"
+
+namespace se {
+
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+
+// ---- causal convolution, silu ----------------------------------------------------------------
+// out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps-1-j), c]); inputs before the entry's first
+// token of this step come from the carried inputs, which are zeros before the request's start.
+// grid (tokens, ceil(C / blockDim)).
+template <typename T>
+__global__ void causal_conv_kernel(const T* x, int pitch, int c0, const float* __restrict__ w,
+                                   const float* __restrict__ bias, const float* state, long long state_pitch,
+                                   int conv_off, const int* __restrict__ token_seq, const int* __restrict__ cu_q,
+                                   const int* __restrict__ seq_rows, float* __restrict__ out, int C, int taps) {
+    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int e = token_seq[t], start = cu_q[e];
+    const float* carried = state + (size_t)seq_rows[e] * state_pitch + conv_off;
+    float acc = bias != nullptr ? bias[c] : 0.f;
+    for (int j = 0; j < taps; ++j) {
+        const int tt = t - (taps - 1 - j);
+        const float v = tt >= start ? to_float(x[(size_t)tt * pitch + c0 + c])
+                                    : carried[(size_t)(taps - 1 - (start - tt)) * C + c];
+        acc += w[(size_t)c * taps + j] * v;
+    }
+    out[(size_t)t * C + c] = silu_f(acc);
+}
+
+// The carried inputs after the step: the last taps-1 inputs of each entry (older ones move up
+// when the entry brought fewer tokens).  grid (entries, ceil(C / blockDim)); runs after the
+// convolution has read the old ones.
+template <typename T>
+__global__ void conv_carry_kernel(const T* x, int pitch, int c0, float* state, long long state_pitch, int conv_off,
+                                  const int* __restrict__ cu_q, const int* __restrict__ seq_rows, int C, int taps) {
+    const int e = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C) return;
+    const int start = cu_q[e], end = cu_q[e + 1], n = end - start;
+    float* carried = state + (size_t)seq_rows[e] * state_pitch + conv_off;
+    for (int i = 0; i < taps - 1; ++i) {          // ascending: slot i + n is read before it is written
+        const int tt = end - (taps - 1) + i;
+        carried[(size_t)i * C + c] = tt >= start ? to_float(x[(size_t)tt * pitch + c0 + c]) : carried[(size_t)(i + n) * C + c];
+    }
+}
+
+// ---- the two recurrences ---------------------------------------------------------------------
+// A block owns (entry, head, tile of value columns).  Thread (column, s) keeps rows s, s + nsplit,
+// ... of its column in registers; nsplit is a power of two <= 32, so a column's threads are
+// neighbouring lanes of one warp and the sums over rows are shuffles.  The inputs of kChunk
+// tokens at a time are staged in shared memory.
+constexpr int kChunk = 8;
+
+__device__ __forceinline__ float split_sum(float v, int nsplit) {
+    for (int o = nsplit >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// Selective state space: S <- exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x.
+// xbc [T, H*P + 2*G*N] holds x | B | C (after convolution and silu); dt_raw is column dt_off + h of
+// the input projection.  y [T, H*P].
+template <typename T, int REGS>
+__global__ void __launch_bounds__(1024)
+ssm_scan_kernel(const float* __restrict__ xbc, const T* proj, int pitch, int dt_off, const float* __restrict__ dt_bias,
+                const float* __restrict__ a_log, const float* __restrict__ d_skip, float* state, long long state_pitch,
+                const int* __restrict__ cu_q, const int* __restrict__ seq_rows, float* __restrict__ y, int H, int P,
+                int N, int G, int nsplit, int cols) {
+    extern __shared__ float sm[];
+    float* sB = sm;                       // [kChunk][N]
+    float* sC = sB + kChunk * N;          // [kChunk][N]
+    float* sx = sC + kChunk * N;          // [kChunk][cols]
+    float* sdt = sx + kChunk * cols;      // [kChunk] step sizes, then [kChunk] decays
+    const int e = blockIdx.x, h = blockIdx.y, g = h / (H / G);
+    const int s = threadIdx.x % nsplit, pl = threadIdx.x / nsplit, p = blockIdx.z * cols + pl;
+    const bool live = p < P;
+    const int start = cu_q[e], end = cu_q[e + 1];
+    const int width = H * P + 2 * G * N;
+    float* Sp = state + (size_t)seq_rows[e] * state_pitch + ((size_t)h * P + (live ? p : 0)) * N;
+    float S[REGS];
+#pragma unroll
+    for (int i = 0; i < REGS; ++i) {
+        const int n = s + nsplit * i;
+        S[i] = live && n < N ? Sp[n] : 0.f;
+    }
+    const float rate = expf(a_log[h]), skip = d_skip[h], bias = dt_bias[h];
+    for (int t0 = start; t0 < end; t0 += kChunk) {
+        const int nt = min(kChunk, end - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * N; i += blockDim.x) {
+            const int c = i / N, n = i - c * N;
+            const float* r = xbc + (size_t)(t0 + c) * width + H * P;
+            sB[c * N + n] = r[g * N + n];
+            sC[c * N + n] = r[G * N + g * N + n];
+        }
+        for (int i = threadIdx.x; i < nt * cols; i += blockDim.x) {
+            const int c = i / cols, j = i - c * cols, pp = blockIdx.z * cols + j;
+            sx[c * cols + j] = pp < P ? xbc[(size_t)(t0 + c) * width + h * P + pp] : 0.f;
+        }
+        if (threadIdx.x < nt) {
+            const float dt = softplus_f(to_float(proj[(size_t)(t0 + threadIdx.x) * pitch + dt_off + h]) + bias);
+            sdt[threadIdx.x] = dt;
+            sdt[kChunk + threadIdx.x] = expf(-rate * dt);
+        }
+        __syncthreads();
+        for (int c = 0; c < nt; ++c) {
+            const float dt = sdt[c], a = sdt[kChunk + c], xv = sx[c * cols + pl];
+            const float bx = dt * xv;
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < REGS; ++i) {
+                const int n = s + nsplit * i;
+                if (n < N) {
+                    S[i] = a * S[i] + sB[c * N + n] * bx;
+                    acc += S[i] * sC[c * N + n];
+                }
+            }
+            acc = split_sum(acc, nsplit);
+            if (s == 0 && live) y[(size_t)(t0 + c) * H * P + h * P + p] = acc + skip * xv;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < REGS; ++i) {
+            const int n = s + nsplit * i;
+            if (n < N) Sp[n] = S[i];
+        }
+    }
+}
+
+// Gated delta rule, per head: S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+// qkv [T, 2*G*d + H*dv] holds q | k | v (q and k already unit vectors, q scaled); dec [T, H*d] the
+// decays g; beta [T, H].  o [T, H*dv].
+template <int REGS>
+__global__ void __launch_bounds__(1024)
+delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ dec, const float* __restrict__ beta,
+                  float* state, long long state_pitch, const int* __restrict__ cu_q, const int* __restrict__ seq_rows,
+                  float* __restrict__ o, int H, int G, int d, int dv, int nsplit, int cols) {
+    extern __shared__ float sm[];
+    float* sq = sm;                       // [kChunk][d]
+    float* sk = sq + kChunk * d;
+    float* sg = sk + kChunk * d;
+    float* sv = sg + kChunk * d;          // [kChunk][cols]
+    float* sb = sv + kChunk * cols;       // [kChunk]
+    const int e = blockIdx.x, h = blockIdx.y, g = h / (H / G);
+    const int s = threadIdx.x % nsplit, jl = threadIdx.x / nsplit, j = blockIdx.z * cols + jl;
+    const bool live = j < dv;
+    const int start = cu_q[e], end = cu_q[e + 1];
+    const int width = 2 * G * d + H * dv;
+    float* Sp = state + (size_t)seq_rows[e] * state_pitch + ((size_t)h * dv + (live ? j : 0)) * d;
+    float S[REGS];
+#pragma unroll
+    for (int i = 0; i < REGS; ++i) {
+        const int n = s + nsplit * i;
+        S[i] = live && n < d ? Sp[n] : 0.f;
+    }
+    for (int t0 = start; t0 < end; t0 += kChunk) {
+        const int nt = min(kChunk, end - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * d; i += blockDim.x) {
+            const int c = i / d, n = i - c * d;
+            const float* r = qkv + (size_t)(t0 + c) * width;
+            sq[c * d + n] = r[g * d + n];
+            sk[c * d + n] = r[G * d + g * d + n];
+            sg[c * d + n] = dec[(size_t)(t0 + c) * H * d + h * d + n];
+        }
+        for (int i = threadIdx.x; i < nt * cols; i += blockDim.x) {
+            const int c = i / cols, jj = i - c * cols, col = blockIdx.z * cols + jj;
+            sv[c * cols + jj] = col < dv ? qkv[(size_t)(t0 + c) * width + 2 * G * d + h * dv + col] : 0.f;
+        }
+        if (threadIdx.x < nt) sb[threadIdx.x] = beta[(size_t)(t0 + threadIdx.x) * H + h];
+        __syncthreads();
+        for (int c = 0; c < nt; ++c) {
+            float r = 0.f;
+#pragma unroll
+            for (int i = 0; i < REGS; ++i) {
+                const int n = s + nsplit * i;
+                if (n < d) {
+                    S[i] *= sg[c * d + n];
+                    r += S[i] * sk[c * d + n];
+                }
+            }
+            r = split_sum(r, nsplit);
+            const float u = sb[c] * (sv[c * cols + jl] - r);
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < REGS; ++i) {
+                const int n = s + nsplit * i;
+                if (n < d) {
+                    S[i] += sk[c * d + n] * u;
+                    acc += S[i] * sq[c * d + n];
+                }
+            }
+            acc = split_sum(acc, nsplit);
+            if (s == 0 && live) o[(size_t)(t0 + c) * H * dv + h * dv + j] = acc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < REGS; ++i) {
+            const int n = s + nsplit * i;
+            if (n < d) Sp[n] = S[i];
+        }
+    }
+}
+
+// ---- prologue of the delta rule ----------------------------------------------------------------
+// One block per token: q and k heads (in qkv, in place) become unit vectors, x / sqrt(sum x^2 +
+// unit_eps), q also times q_scale; dec = exp(-exp(A_log[h]) * softplus(a + dt_bias)); beta =
+// sigmoid(b).  `a` [T, H*d] is the decay projection, `proj` column b_off + h the beta projection.
+template <typename T>
+__global__ void delta_prep_kernel(float* qkv, int width, const T* a, const T* proj, int pitch, int b_off,
+                                  const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                  float* __restrict__ dec, float* __restrict__ beta, int H, int G, int d,
+                                  float unit_eps, float q_scale) {
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    float* row = qkv + (size_t)t * width;
+    for (int hh = warp; hh < 2 * G; hh += warps) {          // q heads, then k heads
+        float* v = row + (size_t)hh * d;
+        float ss = 0.f;
+        for (int i = lane; i < d; i += 32) ss += v[i] * v[i];
+        ss = warp_sum(ss);
+        const float f = (hh < G ? q_scale : 1.f) / sqrtf(ss + unit_eps);
+        for (int i = lane; i < d; i += 32) v[i] *= f;
+    }
+    for (int i = threadIdx.x; i < H * d; i += blockDim.x) {
+        const float rate = expf(a_log[i / d]);
+        dec[(size_t)t * H * d + i] = expf(-rate * softplus_f(to_float(a[(size_t)t * H * d + i]) + dt_bias[i]));
+    }
+    for (int h = threadIdx.x; h < H; h += blockDim.x)
+        beta[(size_t)t * H + h] = sigmoid_f(to_float(proj[(size_t)t * pitch + b_off + h]));
+}
+
+// ---- epilogues ---------------------------------------------------------------------------------
+// Delta rule: each head's output divided by its root mean square over dv, times w[dv] (shared by
+// the heads), times sigmoid(gate).  One warp per (token, head).
+template <typename T>
+__global__ void delta_out_kernel(const float* __restrict__ o, const T* gate, const float* __restrict__ w,
+                                 T* __restrict__ out, int rows, int dv, float eps) {
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= rows) return;
+    const float* v = o + (size_t)r * dv;
+    float ss = 0.f;
+    for (int i = lane; i < dv; i += 32) ss += v[i] * v[i];
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+    for (int i = lane; i < dv; i += 32)
+        out[(size_t)r * dv + i] = from_float<T>(v[i] * inv * w[i] * sigmoid_f(to_float(gate[(size_t)r * dv + i])));
+}
+
+// State space: y * silu(z), then an RMS norm over each of `parts` equal parts of the row, times
+// w.  z is column z_off + i of the input projection.  grid (tokens, parts).
+template <typename T>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* proj, int pitch, int z_off,
+                                        const float* __restrict__ w, T* __restrict__ out, int inner, int parts, float eps) {
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, n = inner / parts, base = blockIdx.y * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = y[(size_t)t * inner + base + i] * silu_f(to_float(proj[(size_t)t * pitch + z_off + base + i]));
+        ss += v * v;
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = y[(size_t)t * inner + base + i] * silu_f(to_float(proj[(size_t)t * pitch + z_off + base + i]));
+        out[(size_t)t * inner + base + i] = from_float<T>(v * inv * w[base + i]);
+    }
+}
+
+// rows of the key/state side a recurrence kernel takes (REGS 16 x 32 lanes)
+constexpr int kMaxStateRows = 512;
+
+static inline void scan_plan(int rows, int columns, int* regs, int* nsplit, int* cols) {
+    *regs = rows > 256 ? 16 : 8;
+    int ns = 1;
+    while (ns * *regs < rows) ns *= 2;
+    *nsplit = ns;
+    int c = 1024 / ns;                         // columns per block: a multiple of 32 / nsplit, at most what is there
+    const int unit = 32 / ns;
+    const int need = (columns + unit - 1) / unit * unit;
+    if (c > need) c = need;
+    *cols = c;
+}
+
+}  // namespace se
+
+extern "C" int se_recurrent_max_state_rows() { return se::kMaxStateRows; }
+
+extern "C" int se_causal_conv(const void* x, int pitch, int c0, const float* w, const float* bias, float* state,
+                              long long state_pitch, int conv_off, const int* token_seq, const int* cu_q,
+                              const int* seq_rows, float* out, int tokens, int entries, int C, int taps, int dtype,
+                              cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (C <= 0 || taps <= 0 || entries <= 0) return SE_ERR_ARGUMENT;
+    const int threads = 128;
+    const dim3 grid(tokens, se::ceil_div(C, threads)), grid2(entries, se::ceil_div(C, threads));
+    if (grid.y > 65535) return SE_ERR_UNSUPPORTED;
+    SE_DISPATCH_DTYPE(dtype, T, {
+        se::causal_conv_kernel<T><<<grid, threads, 0, stream>>>((const T*)x, pitch, c0, w, bias, state, state_pitch, conv_off,
+                                                                token_seq, cu_q, seq_rows, out, C, taps);
+        if (taps > 1)
+            se::conv_carry_kernel<T><<<grid2, threads, 0, stream>>>((const T*)x, pitch, c0, state, state_pitch, conv_off, cu_q,
+                                                                    seq_rows, C, taps);
+    });
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_ssm_scan(const float* xbc, const void* proj, int pitch, int dt_off, const float* dt_bias,
+                           const float* a_log, const float* d_skip, float* state, long long state_pitch, const int* cu_q,
+                           const int* seq_rows, float* y, int entries, int H, int P, int N, int G, int dtype,
+                           cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G) return SE_ERR_ARGUMENT;
+    if (N > se::kMaxStateRows || H > 65535) return SE_ERR_UNSUPPORTED;
+    int regs, nsplit, cols;
+    se::scan_plan(N, P, &regs, &nsplit, &cols);
+    const dim3 grid(entries, H, se::ceil_div(P, cols));
+    const size_t smem = (size_t)(se::kChunk * (2 * N + cols) + 2 * se::kChunk) * sizeof(float);
+    SE_DISPATCH_DTYPE(dtype, T, {
+        if (smem > 40 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(regs == 8 ? se::ssm_scan_kernel<T, 8> : se::ssm_scan_kernel<T, 16>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        if (regs == 8)
+            se::ssm_scan_kernel<T, 8><<<grid, nsplit * cols, smem, stream>>>(xbc, (const T*)proj, pitch, dt_off, dt_bias, a_log,
+                                                                             d_skip, state, state_pitch, cu_q, seq_rows, y, H, P,
+                                                                             N, G, nsplit, cols);
+        else
+            se::ssm_scan_kernel<T, 16><<<grid, nsplit * cols, smem, stream>>>(xbc, (const T*)proj, pitch, dt_off, dt_bias, a_log,
+                                                                              d_skip, state, state_pitch, cu_q, seq_rows, y, H,
+                                                                              P, N, G, nsplit, cols);
+    });
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_delta_prep(float* qkv, const void* a, const void* proj, int pitch, int b_off, const float* dt_bias,
+                             const float* a_log, float* dec, float* beta, int tokens, int H, int G, int d, int dv,
+                             float unit_eps, float q_scale, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0) return SE_ERR_ARGUMENT;
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::delta_prep_kernel<T><<<tokens, 256, 0, stream>>>(qkv, 2 * G * d + H * dv, (const T*)a, (const T*)proj, pitch, b_off,
+                                                            dt_bias, a_log, dec, beta, H, G, d, unit_eps, q_scale));
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_delta_scan(const float* qkv, const float* dec, const float* beta, float* state, long long state_pitch,
+                             const int* cu_q, const int* seq_rows, float* o, int entries, int H, int G, int d, int dv,
+                             cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0) return SE_ERR_ARGUMENT;
+    if (d > se::kMaxStateRows || H > 65535) return SE_ERR_UNSUPPORTED;
+    int regs, nsplit, cols;
+    se::scan_plan(d, dv, &regs, &nsplit, &cols);
+    const dim3 grid(entries, H, se::ceil_div(dv, cols));
+    const size_t smem = (size_t)(se::kChunk * (3 * d + cols) + se::kChunk) * sizeof(float);
+    if (smem > 40 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(regs == 8 ? se::delta_scan_kernel<8> : se::delta_scan_kernel<16>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (regs == 8)
+        se::delta_scan_kernel<8><<<grid, nsplit * cols, smem, stream>>>(qkv, dec, beta, state, state_pitch, cu_q, seq_rows, o, H, G,
+                                                                        d, dv, nsplit, cols);
+    else
+        se::delta_scan_kernel<16><<<grid, nsplit * cols, smem, stream>>>(qkv, dec, beta, state, state_pitch, cu_q, seq_rows, o, H,
+                                                                         G, d, dv, nsplit, cols);
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_delta_out(const float* o, const void* gate, const float* w, void* out, int rows, int dv, float eps,
+                            int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::delta_out_kernel<T><<<se::ceil_div(rows, 4), 128, 0, stream>>>(o, (const T*)gate, w, (T*)out, rows, dv, eps));
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_gated_group_norm(const float* y, const void* proj, int pitch, int z_off, const float* w, void* out,
+                                   int tokens, int inner, int parts, float eps, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (parts <= 0 || inner % parts || parts > 65535) return SE_ERR_ARGUMENT;
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::gated_group_norm_kernel<T><<<dim3(tokens, parts), 256, 0, stream>>>(y, (const T*)proj, pitch, z_off, w, (T*)out, inner,
+                                                                               parts, eps));
+    SE_LAUNCH_CHECK();
+}

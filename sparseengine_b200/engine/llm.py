@@ -101,8 +101,8 @@ class LLM:
         item = torch.empty((), dtype=dt).element_size()
         per_page = 0
         for req, layers in model.layout.groups:
-            per_page = max(per_page, layers * 2 * req.num_kv_heads * cfg.page_size * req.head_dim * item)
-        total_per_page = sum(layers * 2 * req.num_kv_heads * cfg.page_size * req.head_dim * item
+            per_page = max(per_page, layers * cfg.page_size * req.elems_per_token * item)
+        total_per_page = sum(layers * cfg.page_size * req.elems_per_token * item
                              for req, layers in model.layout.groups) or 1
         free, total = torch.cuda.mem_get_info(device)
         spec = model.spec

@@ -58,6 +58,9 @@ class Model:
         self.embed = None
         self.head = None
         self.profile = None     # a dict: CUDA-event pairs per part are collected in it (a debugging aid)
+        self.stream_taps = None  # a list: receives a copy of the residual stream after every schedule entry (a debugging aid)
+        if spec.residual_stream not in ("activation", "float32"):
+            raise ValueError(f"residual_stream {spec.residual_stream!r} is not known ('activation' or 'float32')")
         for i, e in enumerate(spec.order):
             if not 0 <= e.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.blocks)}")
@@ -73,7 +76,8 @@ class Model:
             out.append(Param(self, "head", "head", ParamSpec((s.vocab_size, s.hidden_size)),
                              (Source(s.head_source),)))
         for name, p in self.final_norm.parameters().items():
-            out.append(Param(self.final_norm, name, f"final_norm.{name}", p, (Source(s.final_norm_source),)))
+            source = (s.final_norm_sources or {}).get(name, s.final_norm_source)
+            out.append(Param(self.final_norm, name, f"final_norm.{name}", p, (Source(source),)))
         for i, (block, ls) in enumerate(zip(self.blocks, s.layers)):
             for part_name, part in block.parts().items():
                 for name, p in part.parameters().items():
@@ -157,28 +161,43 @@ class Model:
         """Run the step's tokens through every schedule entry; return logits
         ``[len(want_rows), vocab]`` in the activation dtype, or ``None`` if no row is wanted."""
         s = self.spec
+        stream32 = s.residual_stream == "float32"
         hidden = torch.empty(step.num_tokens, s.hidden_size, dtype=self.dtype, device=step.token_ids.device)
-        ops.embed_gather(self.embed, step.token_ids, hidden)
-        if s.embed_scale != 1.0:
-            hidden.mul_(s.embed_scale)
-        residual = None
+        if stream32:
+            # the stream is 32-bit whatever the activation type; `hidden` is its copy for the matrix products
+            residual = hidden if self.dtype == torch.float32 else torch.empty(hidden.shape, dtype=torch.float32,
+                                                                              device=hidden.device)
+            ops.embed_stream(self.embed, step.token_ids, residual, None if residual is hidden else hidden,
+                             scale=s.embed_scale)
+        else:
+            ops.embed_gather(self.embed, step.token_ids, hidden)
+            if s.embed_scale != 1.0:
+                hidden.mul_(s.embed_scale)
+            residual = None
         for entry, slot in zip(s.order, slots):
             block = self.blocks[entry.layer]
             if self.profile is None:
                 hidden, residual = block.forward(hidden, residual, step, slot)
             else:
                 hidden, residual = self._timed_block(block, hidden, residual, step, slot)
+            if self.stream_taps is not None:
+                self.stream_taps.append((residual if stream32 else hidden).float().clone())
         if want_rows is None or want_rows.numel() == 0:
             return None
         n = want_rows.numel()
-        h = torch.empty(n, s.hidden_size, dtype=self.dtype, device=hidden.device)
-        ops.gather_rows(hidden, want_rows, h)
-        if residual is not None:
-            r = torch.empty_like(h)
+        if stream32:        # the final norm reads the wanted rows of the stream
+            r = torch.empty(n, s.hidden_size, dtype=torch.float32, device=hidden.device)
             ops.gather_rows(residual, want_rows, r)
-            h, _ = self.final_norm.forward(h, r)
+            h, _ = self.final_norm.forward(r)
         else:
-            h, _ = self.final_norm.forward(h)
+            h = torch.empty(n, s.hidden_size, dtype=self.dtype, device=hidden.device)
+            ops.gather_rows(hidden, want_rows, h)
+            if residual is not None:
+                r = torch.empty_like(h)
+                ops.gather_rows(residual, want_rows, r)
+                h, _ = self.final_norm.forward(h, r)
+            else:
+                h, _ = self.final_norm.forward(h)
         logits = linear(h, self.head)
         if s.logit_softcap is not None:
             c = float(s.logit_softcap)

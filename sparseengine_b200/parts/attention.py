@@ -26,7 +26,22 @@ class PagedAttention(Mixer):
         s = spec
         if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
             raise ValueError("num_heads must be a positive multiple of num_kv_heads")
-        if s.head_dim <= 0 or s.head_dim % 16 or s.head_dim > ops.LIMITS["attention_max_head_dim"]:
+        if s.prep not in ("rotary", "general"):
+            raise ValueError(f"attention prep {s.prep!r} is not known ('rotary' or 'general')")
+        self.general = s.prep == "general"
+        if self.general:
+            # no rotation; any head sizes the plain kernels take
+            if not (0 < s.head_dim <= ops.LIMITS["attention_max_head_dim"]
+                    and 0 < s.value_dim <= ops.LIMITS["attention_max_head_dim"]):
+                raise ValueError(f"head sizes {s.head_dim} / {s.value_dim} are not supported (1 to "
+                                 f"{ops.LIMITS['attention_max_head_dim']})")
+            if s.position is not None:
+                raise ValueError("the general preparation has no rotation; leave position unset")
+            if s.q_temperature is not None and not (len(s.q_temperature) == 2 and int(s.q_temperature[1]) > 0):
+                raise ValueError("q_temperature is (coef, every) with every > 0")
+        elif s.v_head_dim not in (None, s.head_dim) or s.q_temperature is not None or not s.own_kv:
+            raise ValueError("v_head_dim, q_temperature and own_kv=False need prep='general'")
+        elif s.head_dim <= 0 or s.head_dim % 16 or s.head_dim > ops.LIMITS["attention_max_head_dim"]:
             raise ValueError(f"head_dim {s.head_dim} is not supported (multiples of 16 up to "
                              f"{ops.LIMITS['attention_max_head_dim']})")
         if s.num_heads > ops.LIMITS["grid_dim_yz"]:
@@ -45,16 +60,37 @@ class PagedAttention(Mixer):
     def parameters(self):
         s = self.spec
         q, kv = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
-        out = {"qkv": ParamSpec((q + 2 * kv, s.hidden_size)), "o": ParamSpec((s.hidden_size, q))}
+        rows = q + (kv + s.num_kv_heads * s.value_dim if s.own_kv else 0)
+        out = {"qkv": ParamSpec((rows, s.hidden_size)), "o": ParamSpec((s.hidden_size, s.num_heads * s.value_dim))}
         if s.qk_norm is not None:
             out["q_norm"] = ParamSpec((q,), "act", "norm")
-            out["k_norm"] = ParamSpec((kv,), "act", "norm")
+            if s.own_kv:
+                out["k_norm"] = ParamSpec((kv,), "act", "norm")
         return out
 
     def kv_request(self):
-        return KVRequest(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+        s = self.spec
+        return KVRequest(s.num_kv_heads, s.head_dim, s.window, None if s.value_dim == s.head_dim else s.value_dim)
+
+    def forward_general(self, x, step, slot):
+        """No rotation: whole-projection norms, query temperature and the page writes in one kernel
+        (32-bit, rounded once); a layer without keys of its own only prepares its queries."""
+        s = self.spec
+        tokens = x.shape[0]
+        proj = linear(x, self.qkv)
+        q = torch.empty(tokens, s.num_heads * s.head_dim, dtype=x.dtype, device=x.device)
+        writes = s.own_kv and slot.write_cache
+        ops.qk_prep_general(proj, self.q_norm, self.k_norm if s.own_kv else None, step.positions, step.token_seq,
+                            step.seq_rows, slot.table, slot.kv, q, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads,
+                            head_dim=s.head_dim, v_head_dim=s.value_dim, eps=s.qk_norm_eps, page_size=slot.page_size,
+                            has_kv=writes, temperature=s.q_temperature)
+        attn = torch.empty(tokens, s.num_heads * s.value_dim, dtype=x.dtype, device=x.device)
+        self.attend(q, attn, step, slot)
+        return linear(attn, self.o)
 
     def forward(self, x, step, slot):
+        if self.general:
+            return self.forward_general(x, step, slot)
         s = self.spec
         tokens = x.shape[0]
         # the position part first: whatever it launches to make its table then lies before the
@@ -97,7 +133,7 @@ class PagedAttention(Mixer):
         """``after_qk_prep``: the kernel launched last is the one that wrote this step's keys and
         ``q``; the split-key kernel then looks its place in the block table up while it still runs."""
         s = self.spec
-        if (self.use_tensor_cores is not False and q.dtype == torch.bfloat16
+        if (self.use_tensor_cores is not False and q.dtype == torch.bfloat16 and s.value_dim == s.head_dim
                 and ops.attn_decode_supported(s.head_dim, s.num_heads, s.num_kv_heads)):
             if not self.takes_portion_kernel(step):
                 max_keys = step.max_kv_len if s.window is None else min(step.max_kv_len, s.window)
@@ -115,7 +151,7 @@ class PagedAttention(Mixer):
             return
         ops.paged_attention_plain(q, slot.kv, slot.table, step.seq_rows, step.token_seq, step.positions, out,
                                   num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
-                                  page_size=slot.page_size, scale=s.scale, window=s.window)
+                                  page_size=slot.page_size, scale=s.scale, window=s.window, v_head_dim=s.value_dim)
 
 
 register_mixer("attention", PagedAttention)

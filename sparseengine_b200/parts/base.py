@@ -33,6 +33,16 @@ class KVRequest:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: every key is kept; n: only the last n
+    v_head_dim: Optional[int] = None # the values' head size where it differs from head_dim
+
+    @property
+    def value_dim(self) -> int:
+        return self.v_head_dim or self.head_dim
+
+    @property
+    def elems_per_token(self) -> int:
+        """Keys and values of one position in one cache layer."""
+        return self.num_kv_heads * (self.head_dim + self.value_dim)
 
 
 @dataclass(frozen=True)
@@ -44,7 +54,9 @@ class StateRequest:
 @dataclass
 class LayerSlot:
     """What one visit of the execution order may touch besides its weights."""
-    kv: Optional[torch.Tensor] = None        # [pages, 2, kv heads, page_size, head_dim] of its cache layer
+    # [pages, 2, kv heads, page_size, head_dim] of its cache layer; with values of another head size
+    # [pages, kv heads * page_size * (head_dim + v_head_dim)]: per page the keys, then the values
+    kv: Optional[torch.Tensor] = None
     table: Optional[torch.Tensor] = None     # [rows, max pages] int32 block table of its group
     page_size: int = 0
     write_cache: bool = True

@@ -9,6 +9,8 @@ another name in ``ARRANGEMENTS``: a class built from ``(LayerSpec, dtype)`` with
 the one that may ask for pages or state), ``forward(hidden, residual, step, slot)`` ->
 ``(hidden, residual)``, and an attribute ``mixer``.  Parts beyond the four of ``pre_norm`` come
 from ``LayerSpec.extra``.
+
+``post_norm`` is the second built-in arrangement (:class:`PostNormBlock`).
 """
 from __future__ import annotations
 
@@ -35,7 +37,43 @@ class PreNormBlock:
         return hidden, residual
 
 
-ARRANGEMENTS = {"pre_norm": PreNormBlock}
+class PostNormBlock:
+    """Norm after the sum, over a 32-bit stream: ``x <- norm(a * x + mixer(x))``, then (if the layer
+    has a feed-forward) ``x <- norm(a * x + feed_forward(x))`` with ``a = residual_scale``.  The block
+    carries ``(x in the activation type, x in 32-bit)``: sublayers read the first, the sums and norms
+    the second (``ModelSpec.residual_stream = "float32"``).  The norms are parts with
+    ``forward_stream`` (``parts.norm.LayerNorm``)."""
+
+    def __init__(self, spec, dtype):
+        self.spec = spec
+        self.alpha = float(spec.residual_scale)
+        self.mixer = make_mixer(spec.mixer, dtype)
+        self.mixer_norm = make_norm(spec.mixer_norm, dtype)
+        self.feed_forward = self.feed_forward_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = make_feed_forward(spec.feed_forward, dtype)
+            self.feed_forward_norm = make_norm(spec.feed_forward_norm, dtype)
+        for n in (self.mixer_norm, self.feed_forward_norm):
+            if n is not None and not hasattr(n, "forward_stream"):
+                raise ValueError("a post-norm block needs norms that work on the 32-bit stream (forward_stream)")
+
+    def parts(self) -> dict:
+        out = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
+        if self.feed_forward is not None:
+            out["feed_forward"] = self.feed_forward
+            out["feed_forward_norm"] = self.feed_forward_norm
+        return out
+
+    def forward(self, hidden, stream, step, slot):
+        y = self.mixer.forward(hidden, step, slot)
+        hidden, stream = self.mixer_norm.forward_stream(stream, y, self.alpha)
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(hidden, step)
+            hidden, stream = self.feed_forward_norm.forward_stream(stream, y, self.alpha)
+        return hidden, stream
+
+
+ARRANGEMENTS = {"pre_norm": PreNormBlock, "post_norm": PostNormBlock}
 
 
 def make_block(spec, dtype):

@@ -1,0 +1,141 @@
+"""Mixers that keep a state of fixed size per request instead of keys and values: a selective
+state-space mixer and a gated delta rule (kernels: csrc/recurrent.cu).
+
+Both ask the cache manager for one 32-bit state row per request (zeroed at admission): the
+recurrence's matrices, then the last ``taps - 1`` inputs of the short causal convolution.  A step
+brings any mix of prompt portions and single tokens; the kernels find each request's tokens and
+state row through the step's device arrays, so the parts run inside replayed CUDA graphs.
+Projections are matrix products in the activation type; what enters a recurrence (step sizes,
+decays, gates of the recurrence, unit norms, the state) is 32-bit.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..config.specs import ParamSpec
+from ..csrc import ops
+from .base import Mixer, StateRequest, register_mixer
+from .linear import linear
+
+
+def _check_state_rows(rows: int, what: str) -> None:
+    if not 0 < rows <= ops.LIMITS["recurrent_max_state_rows"]:
+        raise ValueError(f"{what} {rows} is not supported (1 to {ops.LIMITS['recurrent_max_state_rows']}: a state "
+                         "column's rows live in the registers of one warp's lanes)")
+
+
+class StateSpaceMixer(Mixer):
+    """``[z | x | B | C | dt] = in_proj(h)``; x, B, C through a causal convolution (bias) and silu;
+    ``dt = softplus(dt + dt_bias)``; per head ``S <- exp(-exp(A_log) dt) S + dt B x^T``,
+    ``y = S^T C + D x``; ``y * silu(z)`` RMS-normed in ``norm_groups`` parts, times a weight; out
+    projection."""
+    graph_safe = True
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        s = spec
+        if min(s.num_heads, s.head_dim, s.groups, s.conv_taps, s.norm_groups, s.hidden_size) <= 0:
+            raise ValueError("the sizes of a state-space mixer must be positive")
+        if s.num_heads % s.groups:
+            raise ValueError("num_heads must be a multiple of groups")
+        if (s.num_heads * s.head_dim) % s.norm_groups:
+            raise ValueError("norm_groups must divide num_heads * head_dim")
+        if s.num_heads > ops.LIMITS["grid_dim_yz"] or s.norm_groups > ops.LIMITS["grid_dim_yz"]:
+            raise ValueError("heads and norm groups are grid dimensions of the kernels (at most 65,535)")
+        _check_state_rows(s.state_size, "state_size")
+        self.inner = s.num_heads * s.head_dim
+        self.conv_channels = self.inner + 2 * s.groups * s.state_size
+        self.conv_off = s.num_heads * s.head_dim * s.state_size
+
+    def parameters(self):
+        s = self.spec
+        return {"in_proj": ParamSpec((2 * self.inner + 2 * s.groups * s.state_size + s.num_heads, s.hidden_size)),
+                "conv_w": ParamSpec((self.conv_channels, s.conv_taps), "float32"),
+                "conv_b": ParamSpec((self.conv_channels,), "float32", "bias"),
+                "dt_bias": ParamSpec((s.num_heads,), "float32", "bias"),
+                "a_log": ParamSpec((s.num_heads,), "float32", "bias"),
+                "d_skip": ParamSpec((s.num_heads,), "float32", "norm"),
+                "norm_w": ParamSpec((self.inner,), "float32", "norm"),
+                "o": ParamSpec((s.hidden_size, self.inner))}
+
+    def state_request(self):
+        return StateRequest((self.conv_off + (self.spec.conv_taps - 1) * self.conv_channels,), torch.float32)
+
+    def forward(self, x, step, slot):
+        s = self.spec
+        tokens = x.shape[0]
+        proj = linear(x, self.in_proj)
+        xbc = torch.empty(tokens, self.conv_channels, dtype=torch.float32, device=x.device)
+        ops.causal_conv(proj, self.inner, self.conv_w, self.conv_b, slot.state, self.conv_off, step, xbc)
+        y = torch.empty(tokens, self.inner, dtype=torch.float32, device=x.device)
+        ops.ssm_scan(xbc, proj, self.inner + self.conv_channels, self.dt_bias, self.a_log, self.d_skip, slot.state, step, y,
+                     heads=s.num_heads, head_dim=s.head_dim, state_size=s.state_size, groups=s.groups)
+        gated = torch.empty(tokens, self.inner, dtype=x.dtype, device=x.device)
+        ops.gated_group_norm(y, proj, 0, self.norm_w, gated, parts=s.norm_groups, eps=s.norm_eps)
+        return linear(gated, self.o)
+
+
+class GatedDeltaMixer(Mixer):
+    """``[q | k | v | b | a | g] = in_proj(h)``; q, k, v through causal convolutions and silu; q and
+    k unit vectors per head (q times ``head_dim ** -0.5``); ``beta = sigmoid(b)``; decay per head and key
+    channel ``exp(-exp(A_log) softplus(a2(a) + dt_bias))``; per head ``S <- diag(decay) S``,
+    ``u = beta (v - S^T k)``, ``S <- S + k u^T``, ``o = S^T q``; each head's ``o`` over its root
+    mean square, times a weight shared by the heads, times ``sigmoid(g2(g))``; out projection."""
+    graph_safe = True
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        s = spec
+        if min(s.num_heads, s.num_kv_heads, s.head_dim, s.v_head_dim, s.conv_taps, s.decay_rank, s.gate_rank,
+               s.hidden_size) <= 0:
+            raise ValueError("the sizes of a gated-delta mixer must be positive")
+        if s.num_heads % s.num_kv_heads:
+            raise ValueError("num_heads must be a multiple of num_kv_heads")
+        if s.num_heads > ops.LIMITS["grid_dim_yz"]:
+            raise ValueError("heads are a grid dimension of the kernels (at most 65,535)")
+        _check_state_rows(s.head_dim, "head_dim")
+        self.qk = s.num_kv_heads * s.head_dim
+        self.vv = s.num_heads * s.v_head_dim
+        self.conv_channels = 2 * self.qk + self.vv
+        self.conv_off = s.num_heads * s.v_head_dim * s.head_dim
+        self.b_off = self.conv_channels
+        self.a_off = self.b_off + s.num_heads
+        self.g_off = self.a_off + s.decay_rank
+
+    def parameters(self):
+        s = self.spec
+        return {"in_proj": ParamSpec((self.g_off + s.gate_rank, s.hidden_size)),
+                "conv_w": ParamSpec((self.conv_channels, s.conv_taps), "float32"),
+                "a2": ParamSpec((s.num_heads * s.head_dim, s.decay_rank)),
+                "g2": ParamSpec((self.vv, s.gate_rank)),
+                "dt_bias": ParamSpec((s.num_heads * s.head_dim,), "float32", "bias"),
+                "a_log": ParamSpec((s.num_heads,), "float32", "bias"),
+                "norm_w": ParamSpec((s.v_head_dim,), "float32", "norm"),
+                "o": ParamSpec((s.hidden_size, self.vv))}
+
+    def state_request(self):
+        return StateRequest((self.conv_off + (self.spec.conv_taps - 1) * self.conv_channels,), torch.float32)
+
+    def forward(self, x, step, slot):
+        s = self.spec
+        tokens, dev = x.shape[0], x.device
+        proj = linear(x, self.in_proj)
+        qkv = torch.empty(tokens, self.conv_channels, dtype=torch.float32, device=dev)
+        ops.causal_conv(proj, 0, self.conv_w, None, slot.state, self.conv_off, step, qkv)
+        a = linear(proj[:, self.a_off:self.a_off + s.decay_rank], self.a2)
+        gate = linear(proj[:, self.g_off:self.g_off + s.gate_rank], self.g2)
+        dec = torch.empty(tokens, s.num_heads * s.head_dim, dtype=torch.float32, device=dev)
+        beta = torch.empty(tokens, s.num_heads, dtype=torch.float32, device=dev)
+        ops.delta_prep(qkv, a, proj, self.b_off, self.dt_bias, self.a_log, dec, beta, heads=s.num_heads,
+                       kv_heads=s.num_kv_heads, head_dim=s.head_dim, v_head_dim=s.v_head_dim, unit_eps=s.unit_eps,
+                       q_scale=s.head_dim ** -0.5)
+        o = torch.empty(tokens, self.vv, dtype=torch.float32, device=dev)
+        ops.delta_scan(qkv, dec, beta, slot.state, step, o, heads=s.num_heads, kv_heads=s.num_kv_heads,
+                       head_dim=s.head_dim, v_head_dim=s.v_head_dim)
+        out = torch.empty(tokens, self.vv, dtype=x.dtype, device=dev)
+        ops.delta_out(o, gate, self.norm_w, out, v_head_dim=s.v_head_dim, eps=s.norm_eps)
+        return linear(out, self.o)
+
+
+register_mixer("mamba2", StateSpaceMixer)
+register_mixer("channel_delta", GatedDeltaMixer)

@@ -11,15 +11,16 @@ from .engine.runner import StepEntry
 
 
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, *, page_size: int = 16,
-           max_requests: int = 8, device="cuda:0", lines=(), log=None) -> int:
+           max_requests: int = 4, device="cuda:0", lines=(), log=None) -> int:
     if 64 % page_size:
         raise ValueError("page size must divide 64 (live requests are counted in multiples of 64 tokens)")
     from .csrc import ops
     ops.library()          # compile (first call) and load before anything else; fails loudly
     os.makedirs(out_dir, exist_ok=True)
     num_pages = max(1, -(-max_tokens // page_size))
+    # the pool is made for the live tokens, so no request can be longer than the pool
     runner = build_runner(model_dir, dtype=dtype, page_size=page_size, num_pages=num_pages,
-                          max_rows=max_requests, device=device)
+                          max_rows=max_requests, max_seq_len=num_pages * page_size, device=device)
     for line in lines:
         line = line.strip()
         if not line:
