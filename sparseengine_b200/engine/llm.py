@@ -68,9 +68,9 @@ class LLM:
         self._raw = raw
         dt = resolve_dtype(cfg.dtype)
         from ..config.registry import load_model_spec
-        _, spec = load_model_spec(raw)
-        self.max_model_len = min(cfg.max_model_len or spec.max_position, spec.max_position)
         random = cfg.tiny_random or isinstance(model, dict)
+        _, spec = load_model_spec(raw if random else model)     # a folder also shows its tensors' shapes
+        self.max_model_len = min(cfg.max_model_len or spec.max_position, spec.max_position)
         # weights first; the cache is then sized from what they left
         self.runner = build_runner(
             raw if random else model, dtype=dt, page_size=cfg.page_size,

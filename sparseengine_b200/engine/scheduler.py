@@ -71,11 +71,18 @@ class Scheduler:
         if len(seq.prompt_ids) + seq.params.max_tokens > self.max_model_len:
             raise ValueError(f"prompt ({len(seq.prompt_ids)} tokens) + max_tokens ({seq.params.max_tokens}) "
                              f"exceeds max_model_len ({self.max_model_len})")
-        if self.cache.pages_for_tokens(len(seq.prompt_ids) + 1) > min(g.pool.num_pages for g in self.cache.groups):
+        # a model whose mixers all keep a state of fixed size has no page pool to fit into
+        smallest = min((g.pool.num_pages for g in self.cache.groups), default=None)
+        if smallest is not None and self.cache.pages_for_tokens(len(seq.prompt_ids) + 1) > smallest:
             raise ValueError(f"a prompt of {len(seq.prompt_ids)} tokens does not fit the cache "
-                             f"({min(g.pool.num_pages for g in self.cache.groups)} pages of {self.cache.page_size})")
+                             f"({smallest} pages of {self.cache.page_size})")
         seq.status = Status.WAITING
         self.waiting.append(seq)
+
+    def _pool_text(self) -> str:
+        if not self.cache.groups:
+            return f"no page pool, {self.cache.max_rows} rows"
+        return f"{self.cache.groups[0].pool.num_pages} pages of {self.cache.page_size} tokens"
 
     def is_finished(self) -> bool:
         return not self.waiting and not self.running
@@ -104,7 +111,7 @@ class Scheduler:
             if len(self.running) == 1:
                 raise RuntimeError(
                     f"request {self.running[0].seq_id} cannot take one more token although it has the whole "
-                    f"cache ({self.cache.groups[0].pool.num_pages} pages of {self.cache.page_size}); "
+                    f"cache ({self._pool_text()}); "
                     "the cache is too small for this request")
             victim = self.running[-1]
             self._preempt(victim)
@@ -153,7 +160,7 @@ class Scheduler:
                 s = self.waiting[0]
                 raise RuntimeError(
                     f"request {s.seq_id} ({s.num_tokens} tokens) can never be admitted: the cache has "
-                    f"{self.cache.groups[0].pool.num_pages} pages of {self.cache.page_size} tokens")
+                    f"{self._pool_text()}")
             raise RuntimeError("no runnable work although requests are resident")
         return plan
 

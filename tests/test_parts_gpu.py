@@ -513,4 +513,4 @@ def test_norm_and_position_parts_alone():
     with pytest.raises(ValueError):
         make_position(RotarySpec(rotary_dim=24, pairing="triples"), torch.float32)
     with pytest.raises(ValueError, match="no norm registered"):
-        make_norm(type("S", (), {"kind": "layer_norm"})(), torch.float32)
+        make_norm(type("S", (), {"kind": "batch_norm"})(), torch.float32)
