@@ -16,7 +16,7 @@ import torch
 from ..config.specs import ModelSpec, ParamSpec, Source
 from ..csrc import ops
 from ..parts.base import KVRequest, StateRequest, StepContext, make_norm
-from ..parts.block import PreNormBlock, make_block
+from ..parts.block import PostNormBlock, PreNormBlock, make_block
 from ..parts.linear import linear
 
 
@@ -148,6 +148,13 @@ class Model:
             e1.record()
             self.profile.setdefault(name, []).append((e0, e1))
             return out
+        if isinstance(block, PostNormBlock):
+            y = timed("mixer." + block.mixer.spec.kind, block.mixer.forward, hidden, step, slot)
+            hidden, residual = timed("mixer_norm", block.mixer_norm.forward_stream, residual, y, block.alpha)
+            if block.feed_forward is not None:
+                y = timed("feed_forward", block.feed_forward.forward, hidden, step)
+                hidden, residual = timed("feed_forward_norm", block.feed_forward_norm.forward_stream, residual, y, block.alpha)
+            return hidden, residual
         if not isinstance(block, PreNormBlock):
             return timed("block", block.forward, hidden, residual, step, slot)
         x, residual = timed("mixer_norm", block.mixer_norm.forward, hidden, residual)
