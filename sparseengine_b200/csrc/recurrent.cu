@@ -22,24 +22,41 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 // ---- causal convolution, silu ----------------------------------------------------------------
 // out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps-1-j), c]); inputs before the entry's first
 // token of this step come from the carried inputs, which are zeros before the request's start.
-// grid (tokens, ceil(C / blockDim)).
+// grid (ceil(tokens / kConvTokens), ceil(C / 128)).
+// A block takes kConvTokens consecutive tokens of 128 channels: their inputs (and the taps-1 before
+// them) go to shared memory once, so every input is read from memory once.
+constexpr int kConvTokens = 16;
 template <typename T>
-__global__ void causal_conv_kernel(const T* x, int pitch, int c0, const float* __restrict__ w,
-                                   const float* __restrict__ bias, const float* state, long long state_pitch,
-                                   int conv_off, const int* __restrict__ token_seq, const int* __restrict__ cu_q,
-                                   const int* __restrict__ seq_rows, float* __restrict__ out, int C, int taps) {
-    const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
-    if (c >= C) return;
-    const int e = token_seq[t], start = cu_q[e];
-    const float* carried = state + (size_t)seq_rows[e] * state_pitch + conv_off;
-    float acc = bias != nullptr ? bias[c] : 0.f;
-    for (int j = 0; j < taps; ++j) {
-        const int tt = t - (taps - 1 - j);
-        const float v = tt >= start ? to_float(x[(size_t)tt * pitch + c0 + c])
-                                    : carried[(size_t)(taps - 1 - (start - tt)) * C + c];
-        acc += w[(size_t)c * taps + j] * v;
+__global__ void __launch_bounds__(128)
+causal_conv_kernel(const T* x, int pitch, int c0, const float* __restrict__ w, const float* __restrict__ bias,
+                   const float* state, long long state_pitch, int conv_off, const int* __restrict__ token_seq,
+                   const int* __restrict__ cu_q, const int* __restrict__ seq_rows, float* __restrict__ out, int tokens,
+                   int C, int taps) {
+    extern __shared__ float tile[];           // [kConvTokens + taps - 1][128]
+    const int t0 = blockIdx.x * kConvTokens, c = blockIdx.y * 128 + threadIdx.x;
+    if (c >= C) return;                       // no barrier below: a thread only reads what it wrote itself
+    const int nt = min(kConvTokens, tokens - t0);
+    for (int k = 0; k < nt + taps - 1; ++k) {
+        const int tt = t0 - (taps - 1) + k;
+        tile[k * 128 + threadIdx.x] = tt >= 0 ? to_float(x[(size_t)tt * pitch + c0 + c]) : 0.f;
     }
-    out[(size_t)t * C + c] = silu_f(acc);
+    const float b = bias != nullptr ? bias[c] : 0.f;
+    for (int i = 0; i < nt; ++i) {
+        const int t = t0 + i, e = token_seq[t], start = cu_q[e];
+        float acc = b;
+        if (t - (taps - 1) >= start) {        // the whole window lies in this step's tokens
+            for (int j = 0; j < taps; ++j) acc += w[(size_t)c * taps + j] * tile[(i + j) * 128 + threadIdx.x];
+        } else {
+            const float* carried = state + (size_t)seq_rows[e] * state_pitch + conv_off;
+            for (int j = 0; j < taps; ++j) {
+                const int tt = t - (taps - 1 - j);
+                const float v = tt >= start ? tile[(i + j) * 128 + threadIdx.x]
+                                            : carried[(size_t)(taps - 1 - (start - tt)) * C + c];
+                acc += w[(size_t)c * taps + j] * v;
+            }
+        }
+        out[(size_t)t * C + c] = silu_f(acc);
+    }
 }
 
 // The carried inputs after the step: the last taps-1 inputs of each entry (older ones move up
@@ -60,30 +77,41 @@ __global__ void conv_carry_kernel(const T* x, int pitch, int c0, float* state, l
 
 // ---- the two recurrences ---------------------------------------------------------------------
 // A block owns (entry, head, tile of value columns).  Thread (column, s) keeps rows s, s + nsplit,
-// ... of its column in registers; nsplit is a power of two <= 32, so a column's threads are
-// neighbouring lanes of one warp and the sums over rows are shuffles.  The inputs of kChunk
-// tokens at a time are staged in shared memory.
+// ... (REGS of them) of its column in registers; the nsplit threads of a column (a power of two
+// <= 32) are neighbouring lanes of one warp, so the state moves in coalesced accesses and the
+// sums over rows end in shuffles.  In shared memory a token's row values are regrouped per
+// thread: row n sits at (n % nsplit) * (REGS + 4) + n / nsplit, so a thread reads its values with
+// 16-byte loads and the pad of 4 keeps the threads of a column on different banks.  Rows beyond
+// the state's own are zeros in shared memory and stay zero in the registers, so the inner loops
+// have no bounds.  The inputs of kChunk tokens at a time are staged in shared memory, in two
+// buffers: the copies of the next chunk (cp.async) run while this one is computed.
+//
+// What bounds them is the 32-bit multiply-add rate: two (state space) or four (delta rule)
+// operations per state element and token, in a chain along the tokens of a request.
 constexpr int kChunk = 8;
 
 __device__ __forceinline__ float split_sum(float v, int nsplit) {
     for (int o = nsplit >> 1; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
+__device__ __forceinline__ void copy_async4(float* dst_shared, const float* src) {
+    const unsigned d = (unsigned)__cvta_generic_to_shared(dst_shared);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // Selective state space: S <- exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x.
 // xbc [T, H*P + 2*G*N] holds x | B | C (after convolution and silu); dt_raw is column dt_off + h of
 // the input projection.  y [T, H*P].
 template <typename T, int REGS>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(256)
 ssm_scan_kernel(const float* __restrict__ xbc, const T* proj, int pitch, int dt_off, const float* __restrict__ dt_bias,
                 const float* __restrict__ a_log, const float* __restrict__ d_skip, float* state, long long state_pitch,
                 const int* __restrict__ cu_q, const int* __restrict__ seq_rows, float* __restrict__ y, int H, int P,
                 int N, int G, int nsplit, int cols) {
-    extern __shared__ float sm[];
-    float* sB = sm;                       // [kChunk][N]
-    float* sC = sB + kChunk * N;          // [kChunk][N]
-    float* sx = sC + kChunk * N;          // [kChunk][cols]
-    float* sdt = sx + kChunk * cols;      // [kChunk] step sizes, then [kChunk] decays
+    extern __shared__ __align__(16) float sm[];
+    const int np = nsplit * (REGS + 4);
+    const int buf = kChunk * (2 * np + cols + 2);     // per buffer: B [kChunk][np], C [kChunk][np], x [kChunk][cols], dt, decay
     const int e = blockIdx.x, h = blockIdx.y, g = h / (H / G);
     const int s = threadIdx.x % nsplit, pl = threadIdx.x / nsplit, p = blockIdx.z * cols + pl;
     const bool live = p < P;
@@ -96,41 +124,76 @@ ssm_scan_kernel(const float* __restrict__ xbc, const T* proj, int pitch, int dt_
         const int n = s + nsplit * i;
         S[i] = live && n < N ? Sp[n] : 0.f;
     }
+    for (int i = threadIdx.x; i < 2 * buf; i += blockDim.x) sm[i] = 0.f;      // the rows beyond N stay zero
+    __syncthreads();
     const float rate = expf(a_log[h]), skip = d_skip[h], bias = dt_bias[h];
-    for (int t0 = start; t0 < end; t0 += kChunk) {
-        const int nt = min(kChunk, end - t0);
-        __syncthreads();
+
+    auto issue = [&](int t0, int nt, float* dst) {       // asynchronous copies of a chunk's B, C and x
         for (int i = threadIdx.x; i < nt * N; i += blockDim.x) {
             const int c = i / N, n = i - c * N;
-            const float* r = xbc + (size_t)(t0 + c) * width + H * P;
-            sB[c * N + n] = r[g * N + n];
-            sC[c * N + n] = r[G * N + g * N + n];
+            const float* r = xbc + (size_t)(t0 + c) * width + H * P + g * N + n;
+            const int at = c * np + (n % nsplit) * (REGS + 4) + n / nsplit;
+            copy_async4(dst + at, r);
+            copy_async4(dst + kChunk * np + at, r + G * N);
         }
         for (int i = threadIdx.x; i < nt * cols; i += blockDim.x) {
             const int c = i / cols, j = i - c * cols, pp = blockIdx.z * cols + j;
-            sx[c * cols + j] = pp < P ? xbc[(size_t)(t0 + c) * width + h * P + pp] : 0.f;
+            if (pp < P) copy_async4(dst + 2 * kChunk * np + c * cols + j, xbc + (size_t)(t0 + c) * width + h * P + pp);
         }
-        if (threadIdx.x < nt) {
-            const float dt = softplus_f(to_float(proj[(size_t)(t0 + threadIdx.x) * pitch + dt_off + h]) + bias);
-            sdt[threadIdx.x] = dt;
-            sdt[kChunk + threadIdx.x] = expf(-rate * dt);
+    };
+    auto raw_dt = [&](int t0, int nt) {
+        return (int)threadIdx.x < nt ? to_float(proj[(size_t)(t0 + threadIdx.x) * pitch + dt_off + h]) : 0.f;
+    };
+    auto put_dt = [&](float raw, int nt, float* dst) {
+        if ((int)threadIdx.x < nt) {
+            const float dt = softplus_f(raw + bias);
+            dst[2 * kChunk * np + kChunk * cols + threadIdx.x] = dt;
+            dst[2 * kChunk * np + kChunk * cols + kChunk + threadIdx.x] = expf(-rate * dt);
+        }
+    };
+
+    if (start < end) {
+        const int nt = min(kChunk, end - start);
+        issue(start, nt, sm);
+        put_dt(raw_dt(start, nt), nt, sm);
+        copies_wait();
+    }
+    __syncthreads();
+    int cur = 0;
+    for (int t0 = start; t0 < end; t0 += kChunk, cur ^= 1) {
+        const int nt = min(kChunk, end - t0);
+        const int next_nt = min(kChunk, end - (t0 + kChunk));      // <= 0: this is the last chunk
+        float* here = sm + cur * buf;
+        float* there = sm + (cur ^ 1) * buf;
+        float raw = 0.f;
+        if (next_nt > 0) {
+            issue(t0 + kChunk, next_nt, there);
+            raw = raw_dt(t0 + kChunk, next_nt);
+        }
+        const float* sx = here + 2 * kChunk * np;
+        const float* sdt = sx + kChunk * cols;
+        for (int c = 0; c < nt; ++c) {
+            const float a = sdt[kChunk + c], xv = sx[c * cols + pl];
+            const float bx = sdt[c] * xv;
+            const float4* B4 = reinterpret_cast<const float4*>(here + c * np + s * (REGS + 4));
+            const float4* C4 = reinterpret_cast<const float4*>(here + kChunk * np + c * np + s * (REGS + 4));
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < REGS; i += 4) {
+                const float4 bv = B4[i >> 2], cv = C4[i >> 2];
+                S[i] = a * S[i] + bv.x * bx;         acc[0] += S[i] * cv.x;
+                S[i + 1] = a * S[i + 1] + bv.y * bx; acc[1] += S[i + 1] * cv.y;
+                S[i + 2] = a * S[i + 2] + bv.z * bx; acc[2] += S[i + 2] * cv.z;
+                S[i + 3] = a * S[i + 3] + bv.w * bx; acc[3] += S[i + 3] * cv.w;
+            }
+            const float sum = split_sum((acc[0] + acc[1]) + (acc[2] + acc[3]), nsplit);
+            if (s == 0 && live) y[(size_t)(t0 + c) * H * P + h * P + p] = sum + skip * xv;
+        }
+        if (next_nt > 0) {
+            put_dt(raw, next_nt, there);
+            copies_wait();
         }
         __syncthreads();
-        for (int c = 0; c < nt; ++c) {
-            const float dt = sdt[c], a = sdt[kChunk + c], xv = sx[c * cols + pl];
-            const float bx = dt * xv;
-            float acc = 0.f;
-#pragma unroll
-            for (int i = 0; i < REGS; ++i) {
-                const int n = s + nsplit * i;
-                if (n < N) {
-                    S[i] = a * S[i] + sB[c * N + n] * bx;
-                    acc += S[i] * sC[c * N + n];
-                }
-            }
-            acc = split_sum(acc, nsplit);
-            if (s == 0 && live) y[(size_t)(t0 + c) * H * P + h * P + p] = acc + skip * xv;
-        }
     }
     if (live) {
 #pragma unroll
@@ -145,16 +208,13 @@ ssm_scan_kernel(const float* __restrict__ xbc, const T* proj, int pitch, int dt_
 // qkv [T, 2*G*d + H*dv] holds q | k | v (q and k already unit vectors, q scaled); dec [T, H*d] the
 // decays g; beta [T, H].  o [T, H*dv].
 template <int REGS>
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(256)
 delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ dec, const float* __restrict__ beta,
                   float* state, long long state_pitch, const int* __restrict__ cu_q, const int* __restrict__ seq_rows,
                   float* __restrict__ o, int H, int G, int d, int dv, int nsplit, int cols) {
-    extern __shared__ float sm[];
-    float* sq = sm;                       // [kChunk][d]
-    float* sk = sq + kChunk * d;
-    float* sg = sk + kChunk * d;
-    float* sv = sg + kChunk * d;          // [kChunk][cols]
-    float* sb = sv + kChunk * cols;       // [kChunk]
+    extern __shared__ __align__(16) float sm[];
+    const int np = nsplit * (REGS + 4);
+    const int buf = kChunk * (3 * np + cols + 1);     // per buffer: q, k, g [kChunk][np] each, v [kChunk][cols], beta
     const int e = blockIdx.x, h = blockIdx.y, g = h / (H / G);
     const int s = threadIdx.x % nsplit, jl = threadIdx.x / nsplit, j = blockIdx.z * cols + jl;
     const bool live = j < dv;
@@ -167,46 +227,67 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ dec, 
         const int n = s + nsplit * i;
         S[i] = live && n < d ? Sp[n] : 0.f;
     }
-    for (int t0 = start; t0 < end; t0 += kChunk) {
-        const int nt = min(kChunk, end - t0);
-        __syncthreads();
+    for (int i = threadIdx.x; i < 2 * buf; i += blockDim.x) sm[i] = 0.f;
+    __syncthreads();
+
+    auto issue = [&](int t0, int nt, float* dst) {
         for (int i = threadIdx.x; i < nt * d; i += blockDim.x) {
             const int c = i / d, n = i - c * d;
-            const float* r = qkv + (size_t)(t0 + c) * width;
-            sq[c * d + n] = r[g * d + n];
-            sk[c * d + n] = r[G * d + g * d + n];
-            sg[c * d + n] = dec[(size_t)(t0 + c) * H * d + h * d + n];
+            const float* r = qkv + (size_t)(t0 + c) * width + g * d + n;
+            const int at = c * np + (n % nsplit) * (REGS + 4) + n / nsplit;
+            copy_async4(dst + at, r);
+            copy_async4(dst + kChunk * np + at, r + G * d);
+            copy_async4(dst + 2 * kChunk * np + at, dec + (size_t)(t0 + c) * H * d + h * d + n);
         }
         for (int i = threadIdx.x; i < nt * cols; i += blockDim.x) {
             const int c = i / cols, jj = i - c * cols, col = blockIdx.z * cols + jj;
-            sv[c * cols + jj] = col < dv ? qkv[(size_t)(t0 + c) * width + 2 * G * d + h * dv + col] : 0.f;
+            if (col < dv) copy_async4(dst + 3 * kChunk * np + c * cols + jj, qkv + (size_t)(t0 + c) * width + 2 * G * d + h * dv + col);
         }
-        if (threadIdx.x < nt) sb[threadIdx.x] = beta[(size_t)(t0 + threadIdx.x) * H + h];
-        __syncthreads();
+        if ((int)threadIdx.x < nt) copy_async4(dst + 3 * kChunk * np + kChunk * cols + threadIdx.x, beta + (size_t)(t0 + threadIdx.x) * H + h);
+    };
+
+    if (start < end) {
+        issue(start, min(kChunk, end - start), sm);
+        copies_wait();
+    }
+    __syncthreads();
+    int cur = 0;
+    for (int t0 = start; t0 < end; t0 += kChunk, cur ^= 1) {
+        const int nt = min(kChunk, end - t0);
+        const int next_nt = min(kChunk, end - (t0 + kChunk));
+        float* here = sm + cur * buf;
+        if (next_nt > 0) issue(t0 + kChunk, next_nt, sm + (cur ^ 1) * buf);
+        const float* sv = here + 3 * kChunk * np;
+        const float* sb = sv + kChunk * cols;
         for (int c = 0; c < nt; ++c) {
-            float r = 0.f;
+            const float4* Q4 = reinterpret_cast<const float4*>(here + c * np + s * (REGS + 4));
+            const float4* K4 = reinterpret_cast<const float4*>(here + kChunk * np + c * np + s * (REGS + 4));
+            const float4* G4 = reinterpret_cast<const float4*>(here + 2 * kChunk * np + c * np + s * (REGS + 4));
+            float r[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < REGS; ++i) {
-                const int n = s + nsplit * i;
-                if (n < d) {
-                    S[i] *= sg[c * d + n];
-                    r += S[i] * sk[c * d + n];
-                }
+            for (int i = 0; i < REGS; i += 4) {
+                const float4 gv = G4[i >> 2], kv = K4[i >> 2];
+                S[i] *= gv.x;     r[0] += S[i] * kv.x;
+                S[i + 1] *= gv.y; r[1] += S[i + 1] * kv.y;
+                S[i + 2] *= gv.z; r[2] += S[i + 2] * kv.z;
+                S[i + 3] *= gv.w; r[3] += S[i + 3] * kv.w;
             }
-            r = split_sum(r, nsplit);
-            const float u = sb[c] * (sv[c * cols + jl] - r);
-            float acc = 0.f;
+            const float rs = split_sum((r[0] + r[1]) + (r[2] + r[3]), nsplit);
+            const float u = sb[c] * (sv[c * cols + jl] - rs);
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < REGS; ++i) {
-                const int n = s + nsplit * i;
-                if (n < d) {
-                    S[i] += sk[c * d + n] * u;
-                    acc += S[i] * sq[c * d + n];
-                }
+            for (int i = 0; i < REGS; i += 4) {
+                const float4 kv = K4[i >> 2], qv = Q4[i >> 2];
+                S[i] += kv.x * u;     acc[0] += S[i] * qv.x;
+                S[i + 1] += kv.y * u; acc[1] += S[i + 1] * qv.y;
+                S[i + 2] += kv.z * u; acc[2] += S[i + 2] * qv.z;
+                S[i + 3] += kv.w * u; acc[3] += S[i + 3] * qv.w;
             }
-            acc = split_sum(acc, nsplit);
-            if (s == 0 && live) o[(size_t)(t0 + c) * H * dv + h * dv + j] = acc;
+            const float sum = split_sum((acc[0] + acc[1]) + (acc[2] + acc[3]), nsplit);
+            if (s == 0 && live) o[(size_t)(t0 + c) * H * dv + h * dv + j] = sum;
         }
+        if (next_nt > 0) copies_wait();
+        __syncthreads();
     }
     if (live) {
 #pragma unroll
@@ -264,35 +345,48 @@ __global__ void delta_out_kernel(const float* __restrict__ o, const T* gate, con
 // w.  z is column z_off + i of the input projection.  grid (tokens, parts).
 template <typename T>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* proj, int pitch, int z_off,
-                                        const float* __restrict__ w, T* __restrict__ out, int inner, int parts, float eps) {
+                                        const float* __restrict__ w, T* __restrict__ out, int inner, int parts, float eps,
+                                        int keep) {
+    extern __shared__ float gated[];          // the part's gated values, if they fit (`keep`)
     __shared__ float scratch[33];
     const int t = blockIdx.x, n = inner / parts, base = blockIdx.y * n;
     float ss = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const float v = y[(size_t)t * inner + base + i] * silu_f(to_float(proj[(size_t)t * pitch + z_off + base + i]));
+        if (keep) gated[i] = v;
         ss += v * v;
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)n + eps);
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = y[(size_t)t * inner + base + i] * silu_f(to_float(proj[(size_t)t * pitch + z_off + base + i]));
+        const float v = keep ? gated[i]
+                             : y[(size_t)t * inner + base + i] * silu_f(to_float(proj[(size_t)t * pitch + z_off + base + i]));
         out[(size_t)t * inner + base + i] = from_float<T>(v * inv * w[base + i]);
     }
 }
 
-// rows of the key/state side a recurrence kernel takes (REGS 16 x 32 lanes)
+// rows of the key/state side a recurrence kernel takes (32 registers x 16 lanes)
 constexpr int kMaxStateRows = 512;
 
+// regs: rows a thread keeps (8, 16 or 32: the more, the fewer shuffles and shared-memory reads per
+// multiply-add); nsplit: threads per column; cols: columns per block (a multiple of 32 / nsplit, at
+// most what is there), blocks of 256 threads, so that the columns of a head spread over several
+// blocks and one long request still fills the SMs.
 static inline void scan_plan(int rows, int columns, int* regs, int* nsplit, int* cols) {
-    *regs = rows > 256 ? 16 : 8;
+    *regs = rows > 64 ? 32 : rows > 16 ? 16 : 8;
     int ns = 1;
     while (ns * *regs < rows) ns *= 2;
     *nsplit = ns;
-    int c = 1024 / ns;                         // columns per block: a multiple of 32 / nsplit, at most what is there
+    int c = 256 / ns;
     const int unit = 32 / ns;
     const int need = (columns + unit - 1) / unit * unit;
     if (c > need) c = need;
     *cols = c;
 }
+
+#define SE_SCAN_DISPATCH(regs, ...)                               \
+    if ((regs) == 8) { constexpr int R = 8; __VA_ARGS__; }        \
+    else if ((regs) == 16) { constexpr int R = 16; __VA_ARGS__; } \
+    else { constexpr int R = 32; __VA_ARGS__; }
 
 }  // namespace se
 
@@ -305,11 +399,12 @@ extern "C" int se_causal_conv(const void* x, int pitch, int c0, const float* w, 
     if (tokens <= 0) return 0;
     if (C <= 0 || taps <= 0 || entries <= 0) return SE_ERR_ARGUMENT;
     const int threads = 128;
-    const dim3 grid(tokens, se::ceil_div(C, threads)), grid2(entries, se::ceil_div(C, threads));
-    if (grid.y > 65535) return SE_ERR_UNSUPPORTED;
+    const dim3 grid(se::ceil_div(tokens, se::kConvTokens), se::ceil_div(C, threads)), grid2(entries, se::ceil_div(C, threads));
+    if (grid.y > 65535 || taps > 64) return SE_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)(se::kConvTokens + taps - 1) * 128 * sizeof(float);
     SE_DISPATCH_DTYPE(dtype, T, {
-        se::causal_conv_kernel<T><<<grid, threads, 0, stream>>>((const T*)x, pitch, c0, w, bias, state, state_pitch, conv_off,
-                                                                token_seq, cu_q, seq_rows, out, C, taps);
+        se::causal_conv_kernel<T><<<grid, threads, smem, stream>>>((const T*)x, pitch, c0, w, bias, state, state_pitch, conv_off,
+                                                                   token_seq, cu_q, seq_rows, out, tokens, C, taps);
         if (taps > 1)
             se::conv_carry_kernel<T><<<grid2, threads, 0, stream>>>((const T*)x, pitch, c0, state, state_pitch, conv_off, cu_q,
                                                                     seq_rows, C, taps);
@@ -327,21 +422,17 @@ extern "C" int se_ssm_scan(const float* xbc, const void* proj, int pitch, int dt
     int regs, nsplit, cols;
     se::scan_plan(N, P, &regs, &nsplit, &cols);
     const dim3 grid(entries, H, se::ceil_div(P, cols));
-    const size_t smem = (size_t)(se::kChunk * (2 * N + cols) + 2 * se::kChunk) * sizeof(float);
+    const size_t smem = (size_t)2 * se::kChunk * (2 * nsplit * (regs + 4) + cols + 2) * sizeof(float);
     SE_DISPATCH_DTYPE(dtype, T, {
-        if (smem > 40 * 1024) {
-            cudaError_t e = cudaFuncSetAttribute(regs == 8 ? se::ssm_scan_kernel<T, 8> : se::ssm_scan_kernel<T, 16>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            if (e != cudaSuccess) return (int)e;
-        }
-        if (regs == 8)
-            se::ssm_scan_kernel<T, 8><<<grid, nsplit * cols, smem, stream>>>(xbc, (const T*)proj, pitch, dt_off, dt_bias, a_log,
+        SE_SCAN_DISPATCH(regs, {
+            if (smem > 40 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(se::ssm_scan_kernel<T, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e != cudaSuccess) return (int)e;
+            }
+            se::ssm_scan_kernel<T, R><<<grid, nsplit * cols, smem, stream>>>(xbc, (const T*)proj, pitch, dt_off, dt_bias, a_log,
                                                                              d_skip, state, state_pitch, cu_q, seq_rows, y, H, P,
                                                                              N, G, nsplit, cols);
-        else
-            se::ssm_scan_kernel<T, 16><<<grid, nsplit * cols, smem, stream>>>(xbc, (const T*)proj, pitch, dt_off, dt_bias, a_log,
-                                                                              d_skip, state, state_pitch, cu_q, seq_rows, y, H,
-                                                                              P, N, G, nsplit, cols);
+        });
     });
     SE_LAUNCH_CHECK();
 }
@@ -366,18 +457,15 @@ extern "C" int se_delta_scan(const float* qkv, const float* dec, const float* be
     int regs, nsplit, cols;
     se::scan_plan(d, dv, &regs, &nsplit, &cols);
     const dim3 grid(entries, H, se::ceil_div(dv, cols));
-    const size_t smem = (size_t)(se::kChunk * (3 * d + cols) + se::kChunk) * sizeof(float);
-    if (smem > 40 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(regs == 8 ? se::delta_scan_kernel<8> : se::delta_scan_kernel<16>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    if (regs == 8)
-        se::delta_scan_kernel<8><<<grid, nsplit * cols, smem, stream>>>(qkv, dec, beta, state, state_pitch, cu_q, seq_rows, o, H, G,
+    const size_t smem = (size_t)2 * se::kChunk * (3 * nsplit * (regs + 4) + cols + 1) * sizeof(float);
+    SE_SCAN_DISPATCH(regs, {
+        if (smem > 40 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(se::delta_scan_kernel<R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        se::delta_scan_kernel<R><<<grid, nsplit * cols, smem, stream>>>(qkv, dec, beta, state, state_pitch, cu_q, seq_rows, o, H, G,
                                                                         d, dv, nsplit, cols);
-    else
-        se::delta_scan_kernel<16><<<grid, nsplit * cols, smem, stream>>>(qkv, dec, beta, state, state_pitch, cu_q, seq_rows, o, H,
-                                                                         G, d, dv, nsplit, cols);
+    });
     SE_LAUNCH_CHECK();
 }
 
@@ -393,8 +481,10 @@ extern "C" int se_gated_group_norm(const float* y, const void* proj, int pitch, 
                                    int tokens, int inner, int parts, float eps, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (parts <= 0 || inner % parts || parts > 65535) return SE_ERR_ARGUMENT;
+    const int n = inner / parts, keep = n * (int)sizeof(float) <= 40 * 1024;
+    const int threads = n >= 1024 ? 256 : 128;
     SE_DISPATCH_DTYPE(dtype, T,
-        se::gated_group_norm_kernel<T><<<dim3(tokens, parts), 256, 0, stream>>>(y, (const T*)proj, pitch, z_off, w, (T*)out, inner,
-                                                                               parts, eps));
+        se::gated_group_norm_kernel<T><<<dim3(tokens, parts), threads, keep ? n * sizeof(float) : 0, stream>>>(
+            y, (const T*)proj, pitch, z_off, w, (T*)out, inner, parts, eps, keep));
     SE_LAUNCH_CHECK();
 }

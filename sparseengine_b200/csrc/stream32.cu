@@ -24,7 +24,8 @@ __global__ void embed_stream_kernel(const T* __restrict__ table, const int* __re
     }
 }
 
-// One block per row.  v = alpha * x + y (y optional); out32 and out_act are optional.
+// One block per row.  v = alpha * x + y (y optional); out32 and out_act are optional.  Rows whose
+// width is a multiple of 8 and whose pointers allow it move in groups of 8 elements.
 template <typename T>
 __global__ void add_layernorm_kernel(const float* x, const T* y, float alpha, const T* __restrict__ w,
                                      const T* __restrict__ b, float* out32, T* out_act, int hidden, float eps) {
@@ -33,24 +34,56 @@ __global__ void add_layernorm_kernel(const float* x, const T* y, float alpha, co
     grid_dependency_trigger();
     grid_dependency_wait();
     const size_t base = (size_t)blockIdx.x * hidden;
+    const bool vec = (hidden & 7) == 0 && aligned8(x) && aligned8(w) && (y == nullptr || aligned8(y)) &&
+                     (b == nullptr || aligned8(b)) && (out32 == nullptr || aligned8(out32)) &&
+                     (out_act == nullptr || aligned8(out_act));
     float s = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v = alpha * x[base + i];
-        if (y != nullptr) v += to_float(y[base + i]);
-        row[i] = v;
-        s += v;
+    if (vec) {
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float v[8];
+            load8(x + base + i, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] *= alpha;
+            if (y != nullptr) {
+                float r[8];
+                load8(y + base + i, r);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += r[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { row[i + j] = v[j]; s += v[j]; }
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v = alpha * x[base + i];
+            if (y != nullptr) v += to_float(y[base + i]);
+            row[i] = v;
+            s += v;
+        }
     }
     const float mean = block_sum(s, scratch) / (float)hidden;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {      // block_sum's barriers lie between the writes and here
         const float c = row[i] - mean;
         ss += c * c;
     }
     const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        const float o = (row[i] - mean) * inv * to_float(w[i]) + (b != nullptr ? to_float(b[i]) : 0.f);
-        if (out32 != nullptr) out32[base + i] = o;
-        if (out_act != nullptr) out_act[base + i] = from_float<T>(o);
+    if (vec) {
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float wv[8], bv[8], o[8];
+            load8(w + i, wv);
+            if (b != nullptr) load8(b + i, bv);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] = (row[i + j] - mean) * inv * wv[j] + (b != nullptr ? bv[j] : 0.f);
+            if (out32 != nullptr) store8(out32 + base + i, o);
+            if (out_act != nullptr) store8(out_act + base + i, o);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float o = (row[i] - mean) * inv * to_float(w[i]) + (b != nullptr ? to_float(b[i]) : 0.f);
+            if (out32 != nullptr) out32[base + i] = o;
+            if (out_act != nullptr) out_act[base + i] = from_float<T>(o);
+        }
     }
 }
 
@@ -65,8 +98,20 @@ template <typename T>
 __global__ void activation_kernel(T* x, size_t n, int kind) {
     grid_dependency_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
-        x[i] = from_float<T>(act_apply(to_float(x[i]), kind));
+    const size_t i0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (aligned8(x)) {                        // groups of 8 elements, then the rest one by one
+        const size_t groups = n / 8;
+        for (size_t g = i0; g < groups; g += stride) {
+            float v[8];
+            load8(x + 8 * g, v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = act_apply(v[j], kind);
+            store8(x + 8 * g, v);
+        }
+        for (size_t i = groups * 8 + i0; i < n; i += stride) x[i] = from_float<T>(act_apply(to_float(x[i]), kind));
+        return;
+    }
+    for (size_t i = i0; i < n; i += stride) x[i] = from_float<T>(act_apply(to_float(x[i]), kind));
 }
 
 }  // namespace se
@@ -103,7 +148,8 @@ extern "C" int se_add_layernorm(const float* x, const void* y, float alpha, cons
 extern "C" int se_activation(void* x, long long n, int kind, int dtype, cudaStream_t stream) {
     if (n <= 0) return 0;
     if (kind < 0 || kind > 3) return SE_ERR_ARGUMENT;
-    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    const long long work = (n + 7) / 8;
+    const int blocks = (int)((work + 255) / 256 < 148 * 16 ? (work + 255) / 256 : 148 * 16);
     SE_DISPATCH_DTYPE(dtype, T, {
         cudaError_t e = SE_LAUNCH_DEPENDENT("act", se::activation_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)x, (size_t)n, kind);
         if (e != cudaSuccess) return (int)e;
