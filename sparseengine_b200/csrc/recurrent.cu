@@ -298,6 +298,287 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ dec, 
     }
 }
 
+// ---- the recurrences with a register tile of 8 rows x 4 columns per thread ----------------------
+// One column per thread reads every row value from shared memory once per multiply-add pair, and
+// the shared-memory pipe then sets the pace.  Here a thread keeps 8 rows (s, s + nsplit, ...) of 4
+// neighbouring columns: a row value read once serves 4 columns.  The 4 sums a thread holds are
+// reduced over the nsplit lanes crosswise (lanes trade the halves they do not keep: 2 + 1 shuffles
+// leave one column's sum per lane, then one shuffle per further doubling), not one by one.
+constexpr int kTileRows = 8, kTileCols = 4, kTilePad = kTileRows + 4;
+
+// acc[4] per lane -> the sum over the nsplit lanes of column (2 * (s & 1) + ((s >> 1) & 1)), in every lane;
+// nsplit >= 4
+__device__ __forceinline__ float cross_sum4(const float* acc, int s, int nsplit) {
+    const bool b0 = s & 1, b1 = s & 2;
+    float k0 = b0 ? acc[2] : acc[0], k1 = b0 ? acc[3] : acc[1];
+    k0 += __shfl_xor_sync(0xffffffffu, b0 ? acc[0] : acc[2], 1);
+    k1 += __shfl_xor_sync(0xffffffffu, b0 ? acc[1] : acc[3], 1);
+    float kp = b1 ? k1 : k0;
+    kp += __shfl_xor_sync(0xffffffffu, b1 ? k0 : k1, 2);
+    for (int o = 4; o < nsplit; o <<= 1) kp += __shfl_xor_sync(0xffffffffu, kp, o);
+    return kp;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+ssm_scan_tile_kernel(const float* __restrict__ xbc, const T* proj, int pitch, int dt_off, const float* __restrict__ dt_bias,
+                     const float* __restrict__ a_log, const float* __restrict__ d_skip, float* state, long long state_pitch,
+                     const int* __restrict__ cu_q, const int* __restrict__ seq_rows, float* __restrict__ y, int H, int P,
+                     int N, int G, int nsplit, int cols) {
+    constexpr int RN = kTileRows, RC = kTileCols;
+    extern __shared__ __align__(16) float sm[];
+    const int np = nsplit * kTilePad;
+    const int buf = kChunk * (2 * np + cols + 2);
+    const int e = blockIdx.x, h = blockIdx.y, g = h / (H / G);
+    const int s = threadIdx.x % nsplit, cg = threadIdx.x / nsplit, p0 = blockIdx.z * cols + cg * RC;
+    const int start = cu_q[e], end = cu_q[e + 1];
+    const int width = H * P + 2 * G * N;
+    float* Sp = state + (size_t)seq_rows[e] * state_pitch + (size_t)h * P * N;
+    float S[RN][RC];
+#pragma unroll
+    for (int i = 0; i < RN; ++i)
+#pragma unroll
+        for (int c = 0; c < RC; ++c) {
+            const int n = s + nsplit * i;
+            S[i][c] = (p0 + c < P && n < N) ? Sp[(size_t)(p0 + c) * N + n] : 0.f;
+        }
+    for (int i = threadIdx.x; i < 2 * buf; i += blockDim.x) sm[i] = 0.f;
+    __syncthreads();
+    const float rate = expf(a_log[h]), skip = d_skip[h], bias = dt_bias[h];
+    const int split_log2 = 31 - __clz(nsplit);
+
+    auto issue = [&](int t0, int nt, float* dst) {
+        // no division in here: nsplit is a power of two, and the loops run over rows, then tokens
+        const float* r0 = xbc + (size_t)t0 * width + H * P + g * N;
+        for (int n = threadIdx.x; n < N; n += blockDim.x) {
+            const int at = (n & (nsplit - 1)) * kTilePad + (n >> split_log2);
+            for (int c = 0; c < nt; ++c) {
+                copy_async4(dst + c * np + at, r0 + (size_t)c * width + n);
+                copy_async4(dst + kChunk * np + c * np + at, r0 + (size_t)c * width + G * N + n);
+            }
+        }
+        const float* x0 = xbc + (size_t)t0 * width + h * P + blockIdx.z * cols;
+        for (int j = threadIdx.x; j < cols; j += blockDim.x) {
+            if (blockIdx.z * cols + j < P)
+                for (int c = 0; c < nt; ++c) copy_async4(dst + 2 * kChunk * np + c * cols + j, x0 + (size_t)c * width + j);
+        }
+    };
+    auto raw_dt = [&](int t0, int nt) {
+        return (int)threadIdx.x < nt ? to_float(proj[(size_t)(t0 + threadIdx.x) * pitch + dt_off + h]) : 0.f;
+    };
+    auto put_dt = [&](float raw, int nt, float* dst) {
+        if ((int)threadIdx.x < nt) {
+            const float dt = softplus_f(raw + bias);
+            dst[2 * kChunk * np + kChunk * cols + threadIdx.x] = dt;
+            dst[2 * kChunk * np + kChunk * cols + kChunk + threadIdx.x] = expf(-rate * dt);
+        }
+    };
+    if (start < end) {
+        const int nt = min(kChunk, end - start);
+        issue(start, nt, sm);
+        put_dt(raw_dt(start, nt), nt, sm);
+        copies_wait();
+    }
+    __syncthreads();
+    int cur = 0;
+    for (int t0 = start; t0 < end; t0 += kChunk, cur ^= 1) {
+        const int nt = min(kChunk, end - t0);
+        const int next_nt = min(kChunk, end - (t0 + kChunk));
+        float* here = sm + cur * buf;
+        float* there = sm + (cur ^ 1) * buf;
+        float raw = 0.f;
+        if (next_nt > 0) {
+            issue(t0 + kChunk, next_nt, there);
+            raw = raw_dt(t0 + kChunk, next_nt);
+        }
+        const float* sx = here + 2 * kChunk * np;
+        const float* sdt = sx + kChunk * cols;
+        auto token = [&](int c) {
+            const float a = sdt[kChunk + c], dt = sdt[c];
+            const float4 xv = *reinterpret_cast<const float4*>(sx + c * cols + cg * RC);
+            const float bx[RC] = {dt * xv.x, dt * xv.y, dt * xv.z, dt * xv.w};
+            const float4* B4 = reinterpret_cast<const float4*>(here + c * np + s * kTilePad);
+            const float4* C4 = reinterpret_cast<const float4*>(here + kChunk * np + c * np + s * kTilePad);
+            const float4 b0 = B4[0], b1 = B4[1], c0 = C4[0], c1 = C4[1];
+            const float Bv[RN] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            const float Cv[RN] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+            float acc[RC] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < RN; ++i)
+#pragma unroll
+                for (int k = 0; k < RC; ++k) {
+                    S[i][k] = a * S[i][k] + Bv[i] * bx[k];
+                    acc[k] += S[i][k] * Cv[i];
+                }
+            float* yr = y + (size_t)(t0 + c) * H * P + h * P;
+            if (nsplit >= 4) {
+                const float total = cross_sum4(acc, s, nsplit);
+                const int col = 2 * (s & 1) + ((s >> 1) & 1);
+                if (s < 4 && p0 + col < P) yr[p0 + col] = total + skip * sx[c * cols + cg * RC + col];
+            } else {
+#pragma unroll
+                for (int k = 0; k < RC; ++k) {
+                    const float total = split_sum(acc[k], nsplit);
+                    if (s == 0 && p0 + k < P) yr[p0 + k] = total + skip * sx[c * cols + cg * RC + k];
+                }
+            }
+        };
+        for (int c = 0; c < nt; ++c) token(c);
+        if (next_nt > 0) {
+            put_dt(raw, next_nt, there);
+            copies_wait();
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < RN; ++i)
+#pragma unroll
+        for (int c = 0; c < RC; ++c) {
+            const int n = s + nsplit * i;
+            if (p0 + c < P && n < N) Sp[(size_t)(p0 + c) * N + n] = S[i][c];
+        }
+}
+
+__global__ void __launch_bounds__(256)
+delta_scan_tile_kernel(const float* __restrict__ qkv, const float* __restrict__ dec, const float* __restrict__ beta,
+                       float* state, long long state_pitch, const int* __restrict__ cu_q, const int* __restrict__ seq_rows,
+                       float* __restrict__ o, int H, int G, int d, int dv, int nsplit, int cols) {
+    constexpr int RN = kTileRows, RC = kTileCols;
+    extern __shared__ __align__(16) float sm[];
+    const int np = nsplit * kTilePad;
+    const int buf = kChunk * (3 * np + cols + 1);
+    const int e = blockIdx.x, h = blockIdx.y, g = h / (H / G);
+    const int s = threadIdx.x % nsplit, cg = threadIdx.x / nsplit, j0 = blockIdx.z * cols + cg * RC;
+    const int lane = threadIdx.x & 31;
+    const int start = cu_q[e], end = cu_q[e + 1];
+    const int width = 2 * G * d + H * dv;
+    float* Sp = state + (size_t)seq_rows[e] * state_pitch + (size_t)h * dv * d;
+    float S[RN][RC];
+#pragma unroll
+    for (int i = 0; i < RN; ++i)
+#pragma unroll
+        for (int c = 0; c < RC; ++c) {
+            const int n = s + nsplit * i;
+            S[i][c] = (j0 + c < dv && n < d) ? Sp[(size_t)(j0 + c) * d + n] : 0.f;
+        }
+    for (int i = threadIdx.x; i < 2 * buf; i += blockDim.x) sm[i] = 0.f;
+    __syncthreads();
+    const int split_log2 = 31 - __clz(nsplit);
+
+    auto issue = [&](int t0, int nt, float* dst) {
+        const float* r0 = qkv + (size_t)t0 * width + g * d;
+        const float* g0 = dec + (size_t)t0 * H * d + h * d;
+        for (int n = threadIdx.x; n < d; n += blockDim.x) {
+            const int at = (n & (nsplit - 1)) * kTilePad + (n >> split_log2);
+            for (int c = 0; c < nt; ++c) {
+                copy_async4(dst + c * np + at, r0 + (size_t)c * width + n);
+                copy_async4(dst + kChunk * np + c * np + at, r0 + (size_t)c * width + G * d + n);
+                copy_async4(dst + 2 * kChunk * np + c * np + at, g0 + (size_t)c * H * d + n);
+            }
+        }
+        const float* v0 = qkv + (size_t)t0 * width + 2 * G * d + h * dv + blockIdx.z * cols;
+        for (int jj = threadIdx.x; jj < cols; jj += blockDim.x) {
+            if (blockIdx.z * cols + jj < dv)
+                for (int c = 0; c < nt; ++c) copy_async4(dst + 3 * kChunk * np + c * cols + jj, v0 + (size_t)c * width + jj);
+        }
+        if ((int)threadIdx.x < nt) copy_async4(dst + 3 * kChunk * np + kChunk * cols + threadIdx.x, beta + (size_t)(t0 + threadIdx.x) * H + h);
+    };
+    if (start < end) {
+        issue(start, min(kChunk, end - start), sm);
+        copies_wait();
+    }
+    __syncthreads();
+    int cur = 0;
+    for (int t0 = start; t0 < end; t0 += kChunk, cur ^= 1) {
+        const int nt = min(kChunk, end - t0);
+        const int next_nt = min(kChunk, end - (t0 + kChunk));
+        float* here = sm + cur * buf;
+        if (next_nt > 0) issue(t0 + kChunk, next_nt, sm + (cur ^ 1) * buf);
+        const float* sv = here + 3 * kChunk * np;
+        const float* sb = sv + kChunk * cols;
+        auto token = [&](int c) {
+            const float4* Q4 = reinterpret_cast<const float4*>(here + c * np + s * kTilePad);
+            const float4* K4 = reinterpret_cast<const float4*>(here + kChunk * np + c * np + s * kTilePad);
+            const float4* G4 = reinterpret_cast<const float4*>(here + 2 * kChunk * np + c * np + s * kTilePad);
+            const float4 k0 = K4[0], k1 = K4[1], g0 = G4[0], g1 = G4[1];
+            const float Kv[RN] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w};
+            const float Gv[RN] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            float r[RC] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < RN; ++i)
+#pragma unroll
+                for (int k = 0; k < RC; ++k) {
+                    S[i][k] *= Gv[i];
+                    r[k] += S[i][k] * Kv[i];
+                }
+            float rs[RC];
+            if (nsplit >= 4) {          // one column's sum per lane, then every lane collects the four of its group
+                const float mine = cross_sum4(r, s, nsplit);
+                const int base = lane & ~3;
+                rs[0] = __shfl_sync(0xffffffffu, mine, base);
+                rs[1] = __shfl_sync(0xffffffffu, mine, base | 2);
+                rs[2] = __shfl_sync(0xffffffffu, mine, base | 1);
+                rs[3] = __shfl_sync(0xffffffffu, mine, base | 3);
+            } else {
+#pragma unroll
+                for (int k = 0; k < RC; ++k) rs[k] = split_sum(r[k], nsplit);
+            }
+            const float bt = sb[c];
+            const float4 vv = *reinterpret_cast<const float4*>(sv + c * cols + cg * RC);
+            const float u[RC] = {bt * (vv.x - rs[0]), bt * (vv.y - rs[1]), bt * (vv.z - rs[2]), bt * (vv.w - rs[3])};
+            const float4 q0 = Q4[0], q1 = Q4[1];
+            const float Qv[RN] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+            float acc[RC] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < RN; ++i)
+#pragma unroll
+                for (int k = 0; k < RC; ++k) {
+                    S[i][k] += Kv[i] * u[k];
+                    acc[k] += S[i][k] * Qv[i];
+                }
+            float* orow = o + (size_t)(t0 + c) * H * dv + h * dv;
+            if (nsplit >= 4) {
+                const float total = cross_sum4(acc, s, nsplit);
+                const int col = 2 * (s & 1) + ((s >> 1) & 1);
+                if (s < 4 && j0 + col < dv) orow[j0 + col] = total;
+            } else {
+#pragma unroll
+                for (int k = 0; k < RC; ++k) {
+                    const float total = split_sum(acc[k], nsplit);
+                    if (s == 0 && j0 + k < dv) orow[j0 + k] = total;
+                }
+            }
+        };
+        for (int c = 0; c < nt; ++c) token(c);
+        if (next_nt > 0) copies_wait();
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < RN; ++i)
+#pragma unroll
+        for (int c = 0; c < RC; ++c) {
+            const int n = s + nsplit * i;
+            if (j0 + c < dv && n < d) Sp[(size_t)(j0 + c) * d + n] = S[i][c];
+        }
+}
+
+// Plan of the tiled kernels, for up to 8 * 32 rows: threads per column group, columns per block.
+static inline void tile_plan(int rows, int columns, int units, int* nsplit, int* cols) {
+    int ns = 1;
+    while (ns * kTileRows < rows) ns *= 2;
+    *nsplit = ns;
+    // blocks of 256 threads, smaller ones (down to 64) while (entry, head) pairs x blocks per head would
+    // not give every SM two blocks: one long request then still spreads over the device
+    int threads = 256;
+    while (threads > 256 && (long long)units * (((columns + kTileCols - 1) / kTileCols * ns + threads - 1) / threads) < 2 * 148)
+        threads /= 2;
+    int groups = threads / ns > 0 ? threads / ns : 1;        // column groups per block
+    const int unit = 32 / ns;
+    const int need = ((columns + kTileCols - 1) / kTileCols + unit - 1) / unit * unit;
+    if (groups > need) groups = need;
+    *cols = groups * kTileCols;
+}
+
 // ---- prologue of the delta rule ----------------------------------------------------------------
 // One block per token: q and k heads (in qkv, in place) become unit vectors, x / sqrt(sum x^2 +
 // unit_eps), q also times q_scale; dec = exp(-exp(A_log[h]) * softplus(a + dt_bias)); beta =
@@ -420,6 +701,21 @@ extern "C" int se_ssm_scan(const float* xbc, const void* proj, int pitch, int dt
     if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G) return SE_ERR_ARGUMENT;
     if (N > se::kMaxStateRows || H > 65535) return SE_ERR_UNSUPPORTED;
     int regs, nsplit, cols;
+    if (N <= se::kTileRows * 32) {
+        se::tile_plan(N, P, entries * H, &nsplit, &cols);
+        const dim3 grid(entries, H, se::ceil_div(P, cols));
+        const size_t smem = (size_t)2 * se::kChunk * (2 * nsplit * se::kTilePad + cols + 2) * sizeof(float);
+        SE_DISPATCH_DTYPE(dtype, T, {
+            if (smem > 40 * 1024) {
+                cudaError_t e = cudaFuncSetAttribute(se::ssm_scan_tile_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e != cudaSuccess) return (int)e;
+            }
+            se::ssm_scan_tile_kernel<T><<<grid, nsplit * cols / se::kTileCols, smem, stream>>>(
+                xbc, (const T*)proj, pitch, dt_off, dt_bias, a_log, d_skip, state, state_pitch, cu_q, seq_rows, y, H, P, N, G,
+                nsplit, cols);
+        });
+        SE_LAUNCH_CHECK();
+    }
     se::scan_plan(N, P, &regs, &nsplit, &cols);
     const dim3 grid(entries, H, se::ceil_div(P, cols));
     const size_t smem = (size_t)2 * se::kChunk * (2 * nsplit * (regs + 4) + cols + 2) * sizeof(float);
@@ -455,6 +751,18 @@ extern "C" int se_delta_scan(const float* qkv, const float* dec, const float* be
     if (H <= 0 || G <= 0 || H % G || d <= 0 || dv <= 0) return SE_ERR_ARGUMENT;
     if (d > se::kMaxStateRows || H > 65535) return SE_ERR_UNSUPPORTED;
     int regs, nsplit, cols;
+    if (d <= se::kTileRows * 32) {
+        se::tile_plan(d, dv, entries * H, &nsplit, &cols);
+        const dim3 grid(entries, H, se::ceil_div(dv, cols));
+        const size_t smem = (size_t)2 * se::kChunk * (3 * nsplit * se::kTilePad + cols + 1) * sizeof(float);
+        if (smem > 40 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(se::delta_scan_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        se::delta_scan_tile_kernel<<<grid, nsplit * cols / se::kTileCols, smem, stream>>>(qkv, dec, beta, state, state_pitch, cu_q,
+                                                                                         seq_rows, o, H, G, d, dv, nsplit, cols);
+        SE_LAUNCH_CHECK();
+    }
     se::scan_plan(d, dv, &regs, &nsplit, &cols);
     const dim3 grid(entries, H, se::ceil_div(dv, cols));
     const size_t smem = (size_t)2 * se::kChunk * (3 * nsplit * (regs + 4) + cols + 1) * sizeof(float);
