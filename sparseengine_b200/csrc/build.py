@@ -1,32 +1,33 @@
-"""Compile the CUDA sources of this folder for sm_100a and load them as one library.
+"""Compile the CUDA sources of this folder for sm_100a, each into a shared library of its own.
 
-There is no install step: the first call compiles what is stale (one ``nvcc`` process
-per source, in parallel) into ``_build/`` beside the sources and links
-``libsparseengine_b200.so``; later calls find the objects by the hash of their source
-and flags.  The sources use no framework headers, so a cold build takes well under a
-minute.  If the package folder is not writable the build goes to a per-user folder
-under the system's temporary directory.  There is no fallback: if the library cannot
-be built or loaded, importing the ops raises.
+There is no install step.  Every source is self-contained (the sources share headers, no
+symbols), so a launcher's source is compiled into ``_build/`` beside the sources the first time
+the launcher is used, and later runs find the library by the hash of its source, the headers
+and the flags: a program compiles the kernels its model needs and no more.  ``build()`` compiles
+all of them at once, in parallel (well under a minute; the sources use no framework headers).
+If the package folder is not writable the build goes to a per-user folder under the system's
+temporary directory.  There is no fallback: if a library cannot be built or loaded, the op that
+needs it raises.
 """
 from __future__ import annotations
 
 import ctypes
 import hashlib
 import os
+import re
 import shutil
 import subprocess
 import sys
 import tempfile
 import threading
 import time
-from concurrent.futures import ThreadPoolExecutor
+from concurrent.futures import ThreadPoolExecutor, as_completed
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ARCH_FLAGS + ["-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",
                            "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default"]
 NVCC_FLAGS += os.environ.get("SPARSEENGINE_NVCC_FLAGS", "").split()     # e.g. -D switches for experiments
-LIB_NAME = "libsparseengine_b200.so"
 
 _lock = threading.Lock()
 _lib = None
@@ -74,81 +75,118 @@ def build_dir() -> str:
         return alt
 
 
-def _object_name(src: str, hdr: str) -> str:
+def _library_name(src: str, hdr: str) -> str:
     with open(os.path.join(_HERE, src), "rb") as f:
         digest = hashlib.sha256(f.read() + hdr.encode() + " ".join(NVCC_FLAGS).encode()).hexdigest()[:16]
-    return f"{os.path.splitext(src)[0]}.{digest}.o"
+    return f"{os.path.splitext(src)[0]}.{digest}.so"
 
 
-def _compile_one(nvcc: str, src: str, obj: str) -> None:
-    tmp = f"{obj}.tmp{os.getpid()}"
-    cmd = [nvcc, *NVCC_FLAGS, "-I", _HERE, "-c", os.path.join(_HERE, src), "-o", tmp]
+_EXPORT = re.compile(r'extern\s+"C"\s+[\w\s\*]*?\b(se_\w+)\s*\(')
+_exports = None
+
+
+def exports() -> dict:
+    """Exported launcher name -> the source file that defines it (read from the sources' text)."""
+    global _exports
+    if _exports is None:
+        found = {}
+        for src in sources():
+            with open(os.path.join(_HERE, src)) as f:
+                for name in _EXPORT.findall(f.read()):
+                    found[name] = src
+        _exports = found
+    return _exports
+
+
+def _compile_one(nvcc: str, src: str, lib: str) -> None:
+    tmp = f"{lib}.tmp{os.getpid()}"
+    cmd = [nvcc, *NVCC_FLAGS, "-I", _HERE, "-shared", os.path.join(_HERE, src), "-o", tmp]
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     r = subprocess.run(cmd, capture_output=True, text=True, env=env)
     if r.returncode != 0:
         raise RuntimeError(f"nvcc failed on {src}:\n{' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
-    os.replace(tmp, obj)
-
-
-def build(verbose: bool = True) -> str:
-    """Compile stale sources, link, return the library's path."""
-    out = build_dir()
-    hdr = _headers_digest()
-    srcs = sources()
-    objs = [os.path.join(out, _object_name(s, hdr)) for s in srcs]
-    stale = [(s, o) for s, o in zip(srcs, objs) if not os.path.isfile(o)]
-    link_digest = hashlib.sha256("\n".join(os.path.basename(o) for o in objs).encode()).hexdigest()[:16]
-    lib = os.path.join(out, LIB_NAME)
-    stamp = os.path.join(out, "link.stamp")
-    linked = os.path.isfile(lib) and os.path.isfile(stamp) and open(stamp).read().strip() == link_digest
-    if not stale and linked:
-        return lib
-    nvcc = find_nvcc()
-    if stale:
-        t0 = time.time()
-        if verbose:
-            _say(f"compiling {len(stale)} CUDA source(s) for sm_100a into {out} (first use only)")
-        done = 0
-        with ThreadPoolExecutor(max_workers=min(len(stale), os.cpu_count() or 4)) as pool:
-            futs = {pool.submit(_compile_one, nvcc, s, o): s for s, o in stale}
-            pending = set(futs)
-            while pending:
-                finished = {f for f in pending if f.done()}
-                for f in finished:
-                    f.result()
-                    done += 1
-                    if verbose:
-                        _say(f"  compiled {futs[f]} ({done}/{len(stale)}, {time.time() - t0:.0f}s)")
-                pending -= finished
-                if pending:
-                    time.sleep(0.5)
-                    if verbose and int(time.time() - t0) % 10 == 0 and time.time() - t0 > 9.5:
-                        _say(f"  still compiling ({len(pending)} left, {time.time() - t0:.0f}s)")
-                        time.sleep(0.6)
-    tmp = f"{lib}.tmp{os.getpid()}"
-    cmd = [nvcc, *ARCH_FLAGS, "-shared", "-o", tmp, *objs]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"link failed:\n{' '.join(cmd)}\n{r.stdout}\n{r.stderr}")
     os.replace(tmp, lib)
-    with open(stamp, "w") as f:
-        f.write(link_digest)
-    for f in os.listdir(out):   # drop objects of older source versions
-        if f.endswith(".o") and os.path.join(out, f) not in objs:
+
+
+def _drop_older(out: str, src: str, keep: str) -> None:
+    stem = os.path.splitext(src)[0] + "."
+    for f in os.listdir(out):
+        if f.startswith(stem) and f.endswith((".so", ".o")) and os.path.join(out, f) != keep:
             try:
                 os.remove(os.path.join(out, f))
             except OSError:
                 pass
-    if verbose:
-        _say(f"linked {lib}")
+
+
+def build_source(src: str, verbose: bool = True) -> str:
+    """Compile one source into a shared library of its own, if it is stale; return its path."""
+    out = build_dir()
+    lib = os.path.join(out, _library_name(src, _headers_digest()))
+    if not os.path.isfile(lib):
+        t0 = time.time()
+        if verbose:
+            _say(f"compiling {src} for sm_100a into {out} (first use only)")
+        _compile_one(find_nvcc(), src, lib)
+        _drop_older(out, src, lib)
+        if verbose:
+            _say(f"  compiled {src} ({time.time() - t0:.0f}s)")
     return lib
 
 
-def load() -> ctypes.CDLL:
-    """Build if needed and load the library (once per process)."""
+def build(verbose: bool = True) -> list:
+    """Compile every stale source (in parallel), each into its own shared library; return the
+    libraries' paths.  Nothing needs this call: a launcher's library is compiled when the launcher is
+    first used, so a program compiles what its model needs and no more."""
+    out = build_dir()
+    hdr = _headers_digest()
+    srcs = sources()
+    libs = [os.path.join(out, _library_name(s, hdr)) for s in srcs]
+    stale = [(s, o) for s, o in zip(srcs, libs) if not os.path.isfile(o)]
+    if stale:
+        nvcc = find_nvcc()
+        t0 = time.time()
+        if verbose:
+            _say(f"compiling {len(stale)} CUDA source(s) for sm_100a into {out}")
+        with ThreadPoolExecutor(max_workers=min(len(stale), os.cpu_count() or 4)) as pool:
+            futs = {pool.submit(_compile_one, nvcc, s, o): (s, o) for s, o in stale}
+            for done, f in enumerate(as_completed(futs), 1):
+                f.result()
+                s, o = futs[f]
+                _drop_older(out, s, o)
+                if verbose:
+                    _say(f"  compiled {s} ({done}/{len(stale)}, {time.time() - t0:.0f}s)")
+    return libs
+
+
+class Library:
+    """The launchers of all sources as attributes; a source is compiled (if stale) and loaded when
+    one of its launchers is first asked for."""
+
+    def __init__(self):
+        self._loaded = {}
+
+    def __getattr__(self, name: str):
+        if name.startswith("_"):
+            raise AttributeError(name)
+        src = exports().get(name)
+        if src is None:
+            raise AttributeError(f"no CUDA source of sparseengine_b200 exports {name!r}")
+        with _lock:
+            lib = self._loaded.get(src)
+            if lib is None:
+                lib = self._loaded[src] = ctypes.CDLL(build_source(src), mode=ctypes.RTLD_LOCAL)
+        fn = getattr(lib, name)
+        self.__dict__[name] = fn
+        return fn
+
+    def loaded_sources(self) -> list:
+        return sorted(self._loaded)
+
+
+def load() -> Library:
+    """The library object (once per process).  It compiles nothing by itself."""
     global _lib
-    with _lock:
-        if _lib is None:
-            _lib = ctypes.CDLL(build(), mode=ctypes.RTLD_GLOBAL)
-        return _lib
+    if _lib is None:
+        _lib = Library()
+    return _lib

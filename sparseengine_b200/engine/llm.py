@@ -62,7 +62,6 @@ class LLM:
         check_kernel_tuning(cfg.kernel_tuning)
         device = require_cuda(cfg.device)
         from ..csrc import ops
-        ops.library()       # compile/load the kernels now; there is no other path
         raw = model if isinstance(model, dict) else read_config_json(model)
         raw = cfg.apply_tiny_random_overrides(raw)
         self._raw = raw

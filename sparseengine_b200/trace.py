@@ -15,7 +15,6 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, *, page_si
     if 64 % page_size:
         raise ValueError("page size must divide 64 (live requests are counted in multiples of 64 tokens)")
     from .csrc import ops
-    ops.library()          # compile (first call) and load before anything else; fails loudly
     os.makedirs(out_dir, exist_ok=True)
     num_pages = max(1, -(-max_tokens // page_size))
     # the pool is made for the live tokens, so no request can be longer than the pool
