@@ -22,20 +22,21 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 // ---- causal convolution, silu ----------------------------------------------------------------
 // out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps-1-j), c]); inputs before the entry's first
 // token of this step come from the carried inputs, which are zeros before the request's start.
-// grid (ceil(tokens / kConvTokens), ceil(C / 128)).
-// A block takes kConvTokens consecutive tokens of 128 channels: their inputs (and the taps-1 before
-// them) go to shared memory once, so every input is read from memory once.
+// grid (ceil(tokens / tile), ceil(C / 128)).
+// A block takes `tile` consecutive tokens of 128 channels (up to kConvTokens: the step's mean number of
+// tokens per request, so that a step of single tokens spreads over many blocks): their inputs (and
+// the taps-1 before them) go to shared memory once, so every input is read from memory once.
 constexpr int kConvTokens = 16;
 template <typename T>
 __global__ void __launch_bounds__(128)
 causal_conv_kernel(const T* x, int pitch, int c0, const float* __restrict__ w, const float* __restrict__ bias,
                    const float* state, long long state_pitch, int conv_off, const int* __restrict__ token_seq,
                    const int* __restrict__ cu_q, const int* __restrict__ seq_rows, float* __restrict__ out, int tokens,
-                   int C, int taps) {
-    extern __shared__ float tile[];           // [kConvTokens + taps - 1][128]
-    const int t0 = blockIdx.x * kConvTokens, c = blockIdx.y * 128 + threadIdx.x;
+                   int C, int taps, int tile_tokens) {
+    extern __shared__ float tile[];           // [tile_tokens + taps - 1][128]
+    const int t0 = blockIdx.x * tile_tokens, c = blockIdx.y * 128 + threadIdx.x;
     if (c >= C) return;                       // no barrier below: a thread only reads what it wrote itself
-    const int nt = min(kConvTokens, tokens - t0);
+    const int nt = min(tile_tokens, tokens - t0);
     for (int k = 0; k < nt + taps - 1; ++k) {
         const int tt = t0 - (taps - 1) + k;
         tile[k * 128 + threadIdx.x] = tt >= 0 ? to_float(x[(size_t)tt * pitch + c0 + c]) : 0.f;
@@ -342,8 +343,10 @@ ssm_scan_tile_kernel(const float* __restrict__ xbc, const T* proj, int pitch, in
             const int n = s + nsplit * i;
             S[i][c] = (p0 + c < P && n < N) ? Sp[(size_t)(p0 + c) * N + n] : 0.f;
         }
-    for (int i = threadIdx.x; i < 2 * buf; i += blockDim.x) sm[i] = 0.f;
-    __syncthreads();
+    if (N != nsplit * RN || blockIdx.z * cols + cols > P) {      // rows beyond N and columns beyond P read as zeros
+        for (int i = threadIdx.x; i < 2 * buf; i += blockDim.x) sm[i] = 0.f;
+        __syncthreads();
+    }
     const float rate = expf(a_log[h]), skip = d_skip[h], bias = dt_bias[h];
     const int split_log2 = 31 - __clz(nsplit);
 
@@ -461,8 +464,10 @@ delta_scan_tile_kernel(const float* __restrict__ qkv, const float* __restrict__ 
             const int n = s + nsplit * i;
             S[i][c] = (j0 + c < dv && n < d) ? Sp[(size_t)(j0 + c) * d + n] : 0.f;
         }
-    for (int i = threadIdx.x; i < 2 * buf; i += blockDim.x) sm[i] = 0.f;
-    __syncthreads();
+    if (d != nsplit * RN || blockIdx.z * cols + cols > dv) {     // rows beyond d and columns beyond dv read as zeros
+        for (int i = threadIdx.x; i < 2 * buf; i += blockDim.x) sm[i] = 0.f;
+        __syncthreads();
+    }
     const int split_log2 = 31 - __clz(nsplit);
 
     auto issue = [&](int t0, int nt, float* dst) {
@@ -567,11 +572,12 @@ static inline void tile_plan(int rows, int columns, int units, int* nsplit, int*
     int ns = 1;
     while (ns * kTileRows < rows) ns *= 2;
     *nsplit = ns;
-    // blocks of 256 threads, smaller ones (down to 64) while (entry, head) pairs x blocks per head would
-    // not give every SM two blocks: one long request then still spreads over the device
-    int threads = 256;
-    while (threads > 256 && (long long)units * (((columns + kTileCols - 1) / kTileCols * ns + threads - 1) / threads) < 2 * 148)
-        threads /= 2;
+    // Blocks of 128 threads (SE_SCAN_THREADS, a tuning aid, sets another size): a head's columns spread
+    // over several blocks, so that one long request reaches more SMs, and three such blocks share an
+    // SM, so that one block's state and inputs are on their way while another computes.
+    static const int block_threads = [] { const char* v = ::getenv("SE_SCAN_THREADS"); return v ? atoi(v) : 128; }();
+    const int threads = block_threads < 32 ? 32 : block_threads > 256 ? 256 : block_threads;
+    (void)units;
     int groups = threads / ns > 0 ? threads / ns : 1;        // column groups per block
     const int unit = 32 / ns;
     const int need = ((columns + kTileCols - 1) / kTileCols + unit - 1) / unit * unit;
@@ -680,12 +686,14 @@ extern "C" int se_causal_conv(const void* x, int pitch, int c0, const float* w, 
     if (tokens <= 0) return 0;
     if (C <= 0 || taps <= 0 || entries <= 0) return SE_ERR_ARGUMENT;
     const int threads = 128;
-    const dim3 grid(se::ceil_div(tokens, se::kConvTokens), se::ceil_div(C, threads)), grid2(entries, se::ceil_div(C, threads));
+    int tile = tokens / entries;
+    tile = tile < 1 ? 1 : tile > se::kConvTokens ? se::kConvTokens : tile;
+    const dim3 grid(se::ceil_div(tokens, tile), se::ceil_div(C, threads)), grid2(entries, se::ceil_div(C, threads));
     if (grid.y > 65535 || taps > 64) return SE_ERR_UNSUPPORTED;
-    const size_t smem = (size_t)(se::kConvTokens + taps - 1) * 128 * sizeof(float);
+    const size_t smem = (size_t)(tile + taps - 1) * 128 * sizeof(float);
     SE_DISPATCH_DTYPE(dtype, T, {
         se::causal_conv_kernel<T><<<grid, threads, smem, stream>>>((const T*)x, pitch, c0, w, bias, state, state_pitch, conv_off,
-                                                                   token_seq, cu_q, seq_rows, out, tokens, C, taps);
+                                                                   token_seq, cu_q, seq_rows, out, tokens, C, taps, tile);
         if (taps > 1)
             se::conv_carry_kernel<T><<<grid2, threads, 0, stream>>>((const T*)x, pitch, c0, state, state_pitch, conv_off, cu_q,
                                                                     seq_rows, C, taps);
