@@ -50,6 +50,9 @@ CONFIGS = {
     # head size 128; sizes that are equal or 1; no temperature, no cap
     "ones": config(64, 96, [attn(1, 1, 128, 128, temp=False, ff=64), ssm(1, 64, 128, 1, 2, 1), delta(1, 1, 128, 32, 3, 4, ff=64),
                             ssm(2, 8, 8, 2, 5, 2)], alpha=1.0, scale=1.0, cap=None),
+    # sizes that are multiples of nothing in particular
+    "odd": config(52, 77, [delta(3, 3, 10, 6, 3, 5, ff=50), attn(3, 1, 20, 12, every=9, ff=30), ssm(5, 10, 12, 5, 4, 1),
+                           attn(3, 1, 20, 12, every=11, coef=0.2, kv_from=1)], alpha=3.0, scale=2.0, cap=4.0),
     # no attention at all
     "stateful": config(48, 64, [delta(3, 1, 16, 16, 4, 8, ff=96), ssm(3, 16, 16, 3, 4, 3)]),
 }
