@@ -353,3 +353,36 @@ def test_trace_program(folders, tmp_path):
         got = tu.run_trace_cli(folder, dtype, steps, out, tu.max_live_tokens(steps))
         worst, where = row_errors(got, plain_logits(name, cfg, w, seqs))
         assert worst < BOUND[dtype], (dtype, worst, where)
+
+
+def test_temperature_sampling_through_the_entry_point_is_seeded(folders):
+    """The engine's sampler on this design's logits: the same seed gives the same tokens, another
+    seed others; top-k and top-p keep every token inside what the plain logits allow."""
+    from sparseengine_b200 import LLM, SamplingParams
+    folder, cfg, w = folders["hybrid"]
+    ps = [tu.random_prompt(cfg["vocab"], n, 400 + n) for n in (3, 17, 8)]
+    kw = dict(dtype="float32", page_size=8, num_kvcache_slots=512, max_model_len=128)
+    sp = SamplingParams(temperature=0.9, top_k=5, max_tokens=8, ignore_eos=True)
+    a = [o["token_ids"] for o in LLM(folder, seed=7, **kw).generate(ps, sp)]
+    b = [o["token_ids"] for o in LLM(folder, seed=7, **kw).generate(ps, sp)]
+    c = [o["token_ids"] for o in LLM(folder, seed=8, **kw).generate(ps, sp)]
+    assert a == b and a != c
+    for p, out in zip(ps, a):
+        toks = list(p)
+        for t in out:       # every sampled token is among the five most likely of the plain logits
+            top = torch.topk(pb.forward(cfg, w, toks, torch.float64)[-1], 6).indices.tolist()
+            assert t in top
+            toks.append(t)
+
+
+def test_command_line(folders, tmp_path):
+    import subprocess
+    import sys
+    folder, cfg, w = folders["stateful"]
+    hyper = json.dumps({"dtype": "bfloat16", "page_size": 8, "num_kvcache_slots": 1024, "max_model_len": 256})
+    for extra in ([], ["--tiny_random"]):
+        r = subprocess.run([sys.executable, "-m", "sparseengine_b200.cli.bench", "--model_path", folder, "--lengths", "24",
+                            "--batch_sizes", "3", "--output_len", "6", "--random_prompts", "--generate", "--hyper_params", hyper,
+                            *extra], cwd=tu.ROOT, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert r.stdout.strip()
