@@ -306,6 +306,7 @@ delta_scan_kernel(const float* __restrict__ qkv, const float* __restrict__ dec, 
 // reduced over the nsplit lanes crosswise (lanes trade the halves they do not keep: 2 + 1 shuffles
 // leave one column's sum per lane, then one shuffle per further doubling), not one by one.
 constexpr int kTileRows = 8, kTileCols = 4, kTilePad = kTileRows + 4;
+#define SE_TILE_THREADS 128      // most threads of a block of the tiled kernels (their launch bound)
 
 // acc[4] per lane -> the sum over the nsplit lanes of column (2 * (s & 1) + ((s >> 1) & 1)), in every lane;
 // nsplit >= 4
@@ -321,7 +322,7 @@ __device__ __forceinline__ float cross_sum4(const float* acc, int s, int nsplit)
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(SE_TILE_THREADS)
 ssm_scan_tile_kernel(const float* __restrict__ xbc, const T* proj, int pitch, int dt_off, const float* __restrict__ dt_bias,
                      const float* __restrict__ a_log, const float* __restrict__ d_skip, float* state, long long state_pitch,
                      const int* __restrict__ cu_q, const int* __restrict__ seq_rows, float* __restrict__ y, int H, int P,
@@ -442,7 +443,7 @@ ssm_scan_tile_kernel(const float* __restrict__ xbc, const T* proj, int pitch, in
         }
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(SE_TILE_THREADS)
 delta_scan_tile_kernel(const float* __restrict__ qkv, const float* __restrict__ dec, const float* __restrict__ beta,
                        float* state, long long state_pitch, const int* __restrict__ cu_q, const int* __restrict__ seq_rows,
                        float* __restrict__ o, int H, int G, int d, int dv, int nsplit, int cols) {
@@ -572,11 +573,11 @@ static inline void tile_plan(int rows, int columns, int units, int* nsplit, int*
     int ns = 1;
     while (ns * kTileRows < rows) ns *= 2;
     *nsplit = ns;
-    // Blocks of 128 threads (SE_SCAN_THREADS, a tuning aid, sets another size): a head's columns spread
+    // Blocks of 128 threads (SE_SCAN_THREADS, a tuning aid, sets a smaller size): a head's columns spread
     // over several blocks, so that one long request reaches more SMs, and three such blocks share an
     // SM, so that one block's state and inputs are on their way while another computes.
     static const int block_threads = [] { const char* v = ::getenv("SE_SCAN_THREADS"); return v ? atoi(v) : 128; }();
-    const int threads = block_threads < 32 ? 32 : block_threads > 256 ? 256 : block_threads;
+    const int threads = block_threads < 32 ? 32 : block_threads > SE_TILE_THREADS ? SE_TILE_THREADS : block_threads;
     (void)units;
     int groups = threads / ns > 0 ? threads / ns : 1;        // column groups per block
     const int unit = 32 / ns;
