@@ -560,10 +560,9 @@ def gemm_tc_dense(x, w, out, nt: int = 128):
 # ---- decode attention on tensor cores (bf16; csrc/attention_decode.cu) ----------------------
 
 def attn_decode_supported(head_dim: int, num_heads: int, num_kv_heads: int) -> bool:
-    f = library().se_attn_decode_supported
-    f.restype = _I
-    f.argtypes = [_I, _I, _I]
-    return bool(f(head_dim, num_heads, num_kv_heads))
+    """What ``se_attn_decode_supported`` of the library answers, restated here so that asking does not
+    compile the kernel for a model that cannot use it (a GPU test compares the two)."""
+    return head_dim in (64, 128) and num_kv_heads > 0 and num_heads % num_kv_heads == 0
 
 
 _sm_counts: dict = {}
@@ -638,10 +637,8 @@ def attn_prefill(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, max_q
 
 
 def attn_prefill_tc_supported(head_dim: int, num_heads: int, num_kv_heads: int) -> bool:
-    f = library().se_attn_prefill_tc_supported
-    f.restype = _I
-    f.argtypes = [_I, _I, _I]
-    return bool(f(head_dim, num_heads, num_kv_heads))
+    """What ``se_attn_prefill_tc_supported`` answers (restated, as :func:`attn_decode_supported`)."""
+    return head_dim == 128 and num_kv_heads > 0 and num_heads % num_kv_heads == 0
 
 
 def attn_prefill_tc(q, cache, table, seq_rows, cu_q, kv_len, out, *, entries, max_q_len, num_heads, num_kv_heads,

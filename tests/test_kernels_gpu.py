@@ -905,6 +905,19 @@ def test_qk_prep_pairings_frequency_tables_and_amplitude(dtype, pairing, tokens)
                     num_kv_heads=hkv, head_dim=d, rotary_dim=rot, eps=1e-6, rope_scale=1.0, page_size=page, pairing="x")
 
 
+def test_capability_answers_restated_in_python_are_the_launchers_own():
+    import ctypes
+
+    from sparseengine_b200.csrc import ops
+    for name, fn in (("se_attn_decode_supported", ops.attn_decode_supported),
+                     ("se_attn_prefill_tc_supported", ops.attn_prefill_tc_supported)):
+        f = getattr(ops.library(), name)
+        f.restype, f.argtypes = ctypes.c_int, [ctypes.c_int] * 3
+        for d in (16, 48, 64, 96, 128, 256):
+            for hq, hkv in ((4, 2), (6, 4), (8, 8), (1, 1)):
+                assert bool(f(d, hq, hkv)) == fn(d, hq, hkv), (name, d, hq, hkv)
+
+
 def test_size_limits_the_parts_check_are_the_launchers_own():
     """The limits the parts refuse at construction restate what the launchers refuse; and at a
     limit the kernel runs, one past it the launcher says so."""
