@@ -18,6 +18,10 @@ namespace se {
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+// silu of a value that is rounded to bfloat16 inputs' precision anyway: the fast exponential and
+// division (a few units in the last place of 32-bit) where the activation type is bfloat16
+template <typename T> __device__ __forceinline__ float silu_act(float v) { return silu_f(v); }
+template <> __device__ __forceinline__ float silu_act<__nv_bfloat16>(float v) { return __fdividef(v, 1.f + __expf(-v)); }
 
 // ---- causal convolution, silu ----------------------------------------------------------------
 // out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps-1-j), c]); inputs before the entry's first
@@ -42,11 +46,27 @@ causal_conv_kernel(const T* x, int pitch, int c0, const float* __restrict__ w, c
         tile[k * 128 + threadIdx.x] = tt >= 0 ? to_float(x[(size_t)tt * pitch + c0 + c]) : 0.f;
     }
     const float b = bias != nullptr ? bias[c] : 0.f;
+    // Most tiles lie inside one request's tokens: its first token is then looked up once, not per token.
+    const int e_first = token_seq[t0], e_last = token_seq[t0 + nt - 1];
+    const bool one_entry = e_first == e_last;
+    const int start_first = cu_q[e_first];
+    constexpr int kRegTaps = 8;               // up to this many taps the weights stay in registers
+    float wr[kRegTaps];
+#pragma unroll
+    for (int j = 0; j < kRegTaps; ++j) wr[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
     for (int i = 0; i < nt; ++i) {
-        const int t = t0 + i, e = token_seq[t], start = cu_q[e];
+        const int t = t0 + i;
+        const int e = one_entry ? e_first : token_seq[t];
+        const int start = one_entry ? start_first : cu_q[e];
         float acc = b;
         if (t - (taps - 1) >= start) {        // the whole window lies in this step's tokens
-            for (int j = 0; j < taps; ++j) acc += w[(size_t)c * taps + j] * tile[(i + j) * 128 + threadIdx.x];
+            if (taps <= kRegTaps) {
+#pragma unroll
+                for (int j = 0; j < kRegTaps; ++j)
+                    if (j < taps) acc += wr[j] * tile[(i + j) * 128 + threadIdx.x];
+            } else {
+                for (int j = 0; j < taps; ++j) acc += w[(size_t)c * taps + j] * tile[(i + j) * 128 + threadIdx.x];
+            }
         } else {
             const float* carried = state + (size_t)seq_rows[e] * state_pitch + conv_off;
             for (int j = 0; j < taps; ++j) {
@@ -56,7 +76,7 @@ causal_conv_kernel(const T* x, int pitch, int c0, const float* __restrict__ w, c
                 acc += w[(size_t)c * taps + j] * v;
             }
         }
-        out[(size_t)t * C + c] = silu_f(acc);
+        out[(size_t)t * C + c] = silu_act<T>(acc);
     }
 }
 
