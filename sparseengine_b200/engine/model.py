@@ -151,8 +151,8 @@ class Model:
         if isinstance(block, PostNormBlock):
             y = timed("mixer." + block.mixer.spec.kind, block.mixer.forward, hidden, step, slot)
             hidden, residual = timed("mixer_norm", block.mixer_norm.forward_stream, residual, y, block.alpha)
-            if block.feed_forward is not None:
-                y = timed("feed_forward", block.feed_forward.forward, hidden, step)
+            if block.feed_forward_norm is not None:
+                y = timed("feed_forward", block.feed_forward.forward, hidden, step) if block.feed_forward is not None else None
                 hidden, residual = timed("feed_forward_norm", block.feed_forward_norm.forward_stream, residual, y, block.alpha)
             return hidden, residual
         if not isinstance(block, PreNormBlock):

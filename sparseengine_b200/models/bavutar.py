@@ -43,6 +43,7 @@ class BavutarConfig:
     logit_softcap: Optional[float]
     max_position: int
     ranks: tuple                       # per layer (decay rank, gate rank) or None
+    bare_second_norm: tuple = ()       # layers without feed-forward whose checkpoint still holds a second norm
 
     uses_checkpoint_shapes = True
 
@@ -88,6 +89,10 @@ class BavutarConfig:
                     problems.append(f"layer {i}: the low ranks are given neither by checkpoint tensors "
                                     f"(l{i}.mix.a1, l{i}.mix.g1) nor by the mixer key 'rank'")
             ranks.append(rank)
+        # A layer without feed-forward has no second sublayer.  If a checkpoint holds a second norm for
+        # such a layer all the same, the norm is applied to alpha * x alone.
+        bare = tuple(i for i, layer in enumerate(layers)
+                     if layer.get("mlp") is None and f"l{i}.norm2" in (shapes or {}))
         if problems:
             raise ValueError("Bavutar config.json cannot be used: " + "; ".join(problems))
         cap = raw.get("logit_softcap")
@@ -96,7 +101,8 @@ class BavutarConfig:
                    postln_alpha=float(raw.get("postln_alpha", 1.0)),
                    norm_eps=float((raw.get("norm") or {}).get("eps", 1e-6)),
                    logit_softcap=float(cap) if cap else None,
-                   max_position=int(raw.get("max_position", DEFAULT_MAX_POSITION)), ranks=tuple(ranks))
+                   max_position=int(raw.get("max_position", DEFAULT_MAX_POSITION)), ranks=tuple(ranks),
+                   bare_second_norm=bare)
 
 
 def _attention(cfg, i, m, p):
@@ -160,8 +166,12 @@ def build_bavutar(cfg: BavutarConfig) -> ModelSpec:
             sources["feed_forward.down"] = (Source(f"l{i}.mlp.down"),)
             sources["feed_forward_norm.weight"] = (Source(f"l{i}.norm2"),)
             sources["feed_forward_norm.bias"] = (Source(f"l{i}.norm2.b"),)
+        second_norm = ff is not None or i in cfg.bare_second_norm
+        if ff is None and second_norm:
+            sources["feed_forward_norm.weight"] = (Source(f"l{i}.norm2"),)
+            sources["feed_forward_norm.bias"] = (Source(f"l{i}.norm2.b"),)
         layers.append(LayerSpec(mixer=mixer, feed_forward=ff, mixer_norm=norm,
-                                feed_forward_norm=norm if ff is not None else None, arrangement="post_norm",
+                                feed_forward_norm=norm if second_norm else None, arrangement="post_norm",
                                 residual_scale=cfg.postln_alpha, sources=sources))
         shared = m.get("kv_from") if layer["type"] == "attention" else None
         order.append(ScheduleEntry(layer=i, cache=shared, write_cache=shared is None))

@@ -39,7 +39,8 @@ class PreNormBlock:
 
 class PostNormBlock:
     """Norm after the sum, over a 32-bit stream: ``x <- norm(a * x + mixer(x))``, then (if the layer
-    has a feed-forward) ``x <- norm(a * x + feed_forward(x))`` with ``a = residual_scale``.  The block
+    has a feed-forward) ``x <- norm(a * x + feed_forward(x))`` with ``a = residual_scale``; a layer spec
+    with a second norm but no feed-forward gets ``x <- norm(a * x)``.  The block
     carries ``(x in the activation type, x in 32-bit)``: sublayers read the first, the sums and norms
     the second (``ModelSpec.residual_stream = "float32"``).  The norms are parts with
     ``forward_stream`` (``parts.norm.LayerNorm``)."""
@@ -52,6 +53,7 @@ class PostNormBlock:
         self.feed_forward = self.feed_forward_norm = None
         if spec.feed_forward is not None:
             self.feed_forward = make_feed_forward(spec.feed_forward, dtype)
+        if spec.feed_forward_norm is not None:      # without a feed-forward: the norm of a * x alone
             self.feed_forward_norm = make_norm(spec.feed_forward_norm, dtype)
         for n in (self.mixer_norm, self.feed_forward_norm):
             if n is not None and not hasattr(n, "forward_stream"):
@@ -61,14 +63,15 @@ class PostNormBlock:
         out = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
         if self.feed_forward is not None:
             out["feed_forward"] = self.feed_forward
+        if self.feed_forward_norm is not None:
             out["feed_forward_norm"] = self.feed_forward_norm
         return out
 
     def forward(self, hidden, stream, step, slot):
         y = self.mixer.forward(hidden, step, slot)
         hidden, stream = self.mixer_norm.forward_stream(stream, y, self.alpha)
-        if self.feed_forward is not None:
-            y = self.feed_forward.forward(hidden, step)
+        if self.feed_forward_norm is not None:
+            y = self.feed_forward.forward(hidden, step) if self.feed_forward is not None else None
             hidden, stream = self.feed_forward_norm.forward_stream(stream, y, self.alpha)
         return hidden, stream
 

@@ -386,3 +386,34 @@ def test_command_line(folders, tmp_path):
                             *extra], cwd=tu.ROOT, capture_output=True, text=True, timeout=300)
         assert r.returncode == 0, r.stderr[-2000:]
         assert r.stdout.strip()
+
+
+def test_a_second_norm_without_a_feed_forward(tmp_path):
+    """A layer without feed-forward has no second sublayer; a checkpoint that holds a second norm for
+    it all the same gets that norm applied to alpha * x alone."""
+    from safetensors.torch import save_file
+    cfg = config(40, 48, [ssm(2, 8, 8, 1, 3, 1), attn(2, 1, 16, 16, every=4, ff=48)], cap=None)
+    w = pb.random_weights(cfg, 23)
+    w["l0.norm2"] = (1.0 + 0.1 * torch.randn(40)).to(torch.bfloat16)
+    w["l0.norm2.b"] = (0.1 * torch.randn(40)).to(torch.bfloat16)
+    with open(tmp_path / "config.json", "w") as f:
+        json.dump(cfg, f)
+    save_file({k: v.contiguous() for k, v in w.items()}, str(tmp_path / "model.safetensors"))
+    toks = tu.random_prompt(48, 19, 5)
+    # plain: layer 0, then its bare second norm, then the rest
+    wd = {k: v.double() for k, v in w.items()}
+    x = wd["embed"][torch.tensor(toks)] * cfg["embedding"]["scale"]
+    a, eps = cfg["postln_alpha"], cfg["norm"]["eps"]
+    x = pb.layer_norm(a * x + pb.mamba2(x, wd, "l0.mix.", cfg["layers"][0]["mixer"], eps), wd["l0.norm1"], wd["l0.norm1.b"], eps)
+    x = pb.layer_norm(a * x, wd["l0.norm2"], wd["l0.norm2.b"], eps)
+    m = cfg["layers"][1]["mixer"]
+    y = pb.attention(x, wd, "l1.mix.", m, eps, *pb.attention_keys_values(x, wd, "l1.mix.", m, eps))
+    x = pb.layer_norm(a * x + y, wd["l1.norm1"], wd["l1.norm1.b"], eps)
+    x = pb.layer_norm(a * x + pb.feed_forward(x, wd, "l1.mlp."), wd["l1.norm2"], wd["l1.norm2.b"], eps)
+    ref = (pb.layer_norm(x, wd["final.norm"], wd["final.norm.b"], eps) @ wd["head"].T).float().numpy()
+    seqs = {"s": toks}
+    steps = tu.trace_chunks(seqs, sizes=(5, 2, 7))
+    runner = make_runner(str(tmp_path), "float32", steps)
+    got = tu.run_trace_runner(runner, steps)
+    worst, where = row_errors(got, {"s": ref})
+    assert worst < BOUND["float32"], (worst, where)
