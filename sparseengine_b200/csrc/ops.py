@@ -26,7 +26,7 @@ _fns: dict = {}
 
 # Kernels launched through these bindings since the process started (a launcher that
 # starts two kernels counts two).  Benchmarks read the difference around a timed region.
-KERNELS_PER_CALL = {"se_attn_decode": 2, "se_router": 2, "se_causal_conv": 2}   # upper bounds per call
+KERNELS_PER_CALL = {"se_attn_decode": 2, "se_router": 2, "se_causal_conv": 2, "se_ssm_scan": 2}   # upper bounds per call
 launch_count = 0
 calls: dict = {}     # launcher name -> times called (tests check which kernels a path took)
 
@@ -273,11 +273,13 @@ def causal_conv(x, c0: int, w, bias, state, conv_off: int, step, out):
 
 
 def ssm_scan(xbc, proj, dt_off: int, dt_bias, a_log, d_skip, state, step, y, *, heads, head_dim, state_size, groups):
-    _check(_fn("se_ssm_scan", "ppii" "ppp" "pl" "pp" "p" "iiiii" "ip")(
+    tokens = xbc.shape[0]
+    steps = torch.empty(tokens, heads, 2, dtype=torch.float32, device=xbc.device)     # step sizes and decays
+    _check(_fn("se_ssm_scan", "ppii" "ppp" "pl" "pp" "pp" "iiiiii" "ip")(
         _ptr(xbc, torch.float32, "xbc"), proj.data_ptr(), proj.stride(0), int(dt_off), _ptr(dt_bias, torch.float32),
         _ptr(a_log, torch.float32), _ptr(d_skip, torch.float32), _ptr(state, torch.float32, "state"), state.stride(0),
-        _ptr(step.cu_q), _ptr(step.seq_rows), _ptr(y, torch.float32, "y"), step.num_seqs, heads, head_dim, state_size,
-        groups, dtype_code(proj.dtype), _stream()), "ssm_scan")
+        _ptr(step.cu_q), _ptr(step.seq_rows), _ptr(y, torch.float32, "y"), _ptr(steps), tokens, step.num_seqs, heads,
+        head_dim, state_size, groups, dtype_code(proj.dtype), _stream()), "ssm_scan")
     return y
 
 

@@ -341,16 +341,29 @@ __device__ __forceinline__ float cross_sum4(const float* acc, int s, int nsplit)
     return kp;
 }
 
+// Step sizes and decays of the state-space recurrence, [T, H, 2] = (softplus(raw + bias),
+// exp(-exp(A_log) * that)): taken out of the recurrence, where one warp computed them while the
+// others waited.
+template <typename T>
+__global__ void ssm_steps_kernel(const T* proj, int pitch, int dt_off, const float* __restrict__ dt_bias,
+                                 const float* __restrict__ a_log, float* __restrict__ steps, int tokens, int H) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= tokens * H) return;
+    const int t = i / H, h = i - t * H;
+    const float dt = softplus_f(to_float(proj[(size_t)t * pitch + dt_off + h]) + dt_bias[h]);
+    steps[2 * (size_t)i] = dt;
+    steps[2 * (size_t)i + 1] = expf(-expf(a_log[h]) * dt);
+}
+
 template <typename T>
 __global__ void __launch_bounds__(SE_TILE_THREADS)
-ssm_scan_tile_kernel(const float* __restrict__ xbc, const T* proj, int pitch, int dt_off, const float* __restrict__ dt_bias,
-                     const float* __restrict__ a_log, const float* __restrict__ d_skip, float* state, long long state_pitch,
-                     const int* __restrict__ cu_q, const int* __restrict__ seq_rows, float* __restrict__ y, int H, int P,
-                     int N, int G, int nsplit, int cols) {
+ssm_scan_tile_kernel(const float* __restrict__ xbc, const float* __restrict__ steps, const float* __restrict__ d_skip,
+                     float* state, long long state_pitch, const int* __restrict__ cu_q, const int* __restrict__ seq_rows,
+                     float* __restrict__ y, int H, int P, int N, int G, int nsplit, int cols) {
     constexpr int RN = kTileRows, RC = kTileCols;
     extern __shared__ __align__(16) float sm[];
     const int np = nsplit * kTilePad;
-    const int buf = kChunk * (2 * np + cols + 2);
+    const int buf = kChunk * (2 * np + cols + 2);     // per buffer: B, C [kChunk][np], x [kChunk][cols], (step, decay) [kChunk][2]
     const int e = blockIdx.x, h = blockIdx.y, g = h / (H / G);
     const int s = threadIdx.x % nsplit, cg = threadIdx.x / nsplit, p0 = blockIdx.z * cols + cg * RC;
     const int start = cu_q[e], end = cu_q[e + 1];
@@ -368,7 +381,7 @@ ssm_scan_tile_kernel(const float* __restrict__ xbc, const T* proj, int pitch, in
         for (int i = threadIdx.x; i < 2 * buf; i += blockDim.x) sm[i] = 0.f;
         __syncthreads();
     }
-    const float rate = expf(a_log[h]), skip = d_skip[h], bias = dt_bias[h];
+    const float skip = d_skip[h];
     const int split_log2 = 31 - __clz(nsplit);
 
     auto issue = [&](int t0, int nt, float* dst) {
@@ -386,39 +399,27 @@ ssm_scan_tile_kernel(const float* __restrict__ xbc, const T* proj, int pitch, in
             if (blockIdx.z * cols + j < P)
                 for (int c = 0; c < nt; ++c) copy_async4(dst + 2 * kChunk * np + c * cols + j, x0 + (size_t)c * width + j);
         }
-    };
-    auto raw_dt = [&](int t0, int nt) {
-        return (int)threadIdx.x < nt ? to_float(proj[(size_t)(t0 + threadIdx.x) * pitch + dt_off + h]) : 0.f;
-    };
-    auto put_dt = [&](float raw, int nt, float* dst) {
-        if ((int)threadIdx.x < nt) {
-            const float dt = softplus_f(raw + bias);
-            dst[2 * kChunk * np + kChunk * cols + threadIdx.x] = dt;
-            dst[2 * kChunk * np + kChunk * cols + kChunk + threadIdx.x] = expf(-rate * dt);
-        }
+        if ((int)threadIdx.x < 2 * nt)
+            copy_async4(dst + 2 * kChunk * np + kChunk * cols + threadIdx.x,
+                        steps + 2 * ((size_t)(t0 + (threadIdx.x >> 1)) * H + h) + (threadIdx.x & 1));
     };
     if (start < end) {
-        const int nt = min(kChunk, end - start);
-        issue(start, nt, sm);
-        put_dt(raw_dt(start, nt), nt, sm);
+        issue(start, min(kChunk, end - start), sm);
         copies_wait();
     }
     __syncthreads();
+    const int col = 2 * (s & 1) + ((s >> 1) & 1);      // the column whose sum the crosswise reduction leaves in this lane
     int cur = 0;
     for (int t0 = start; t0 < end; t0 += kChunk, cur ^= 1) {
         const int nt = min(kChunk, end - t0);
         const int next_nt = min(kChunk, end - (t0 + kChunk));
-        float* here = sm + cur * buf;
-        float* there = sm + (cur ^ 1) * buf;
-        float raw = 0.f;
-        if (next_nt > 0) {
-            issue(t0 + kChunk, next_nt, there);
-            raw = raw_dt(t0 + kChunk, next_nt);
-        }
+        const float* here = sm + cur * buf;
+        if (next_nt > 0) issue(t0 + kChunk, next_nt, sm + (cur ^ 1) * buf);
         const float* sx = here + 2 * kChunk * np;
-        const float* sdt = sx + kChunk * cols;
-        auto token = [&](int c) {
-            const float a = sdt[kChunk + c], dt = sdt[c];
+        const float* sdt = sx + kChunk * cols;         // (step, decay) per token
+        // One token: its inputs from shared memory, the state update, the four column sums.
+        auto advance = [&](int c, float* sums) {
+            const float a = sdt[2 * c + 1], dt = sdt[2 * c];
             const float4 xv = *reinterpret_cast<const float4*>(sx + c * cols + cg * RC);
             const float bx[RC] = {dt * xv.x, dt * xv.y, dt * xv.z, dt * xv.w};
             const float4* B4 = reinterpret_cast<const float4*>(here + c * np + s * kTilePad);
@@ -426,32 +427,45 @@ ssm_scan_tile_kernel(const float* __restrict__ xbc, const T* proj, int pitch, in
             const float4 b0 = B4[0], b1 = B4[1], c0 = C4[0], c1 = C4[1];
             const float Bv[RN] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
             const float Cv[RN] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-            float acc[RC] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int k = 0; k < RC; ++k) sums[k] = 0.f;
 #pragma unroll
             for (int i = 0; i < RN; ++i)
 #pragma unroll
                 for (int k = 0; k < RC; ++k) {
                     S[i][k] = a * S[i][k] + Bv[i] * bx[k];
-                    acc[k] += S[i][k] * Cv[i];
+                    sums[k] += S[i][k] * Cv[i];
                 }
+        };
+        auto finish = [&](int c, const float* sums) {       // the sums over the lanes, and the output
             float* yr = y + (size_t)(t0 + c) * H * P + h * P;
             if (nsplit >= 4) {
-                const float total = cross_sum4(acc, s, nsplit);
-                const int col = 2 * (s & 1) + ((s >> 1) & 1);
+                const float total = cross_sum4(sums, s, nsplit);
                 if (s < 4 && p0 + col < P) yr[p0 + col] = total + skip * sx[c * cols + cg * RC + col];
             } else {
 #pragma unroll
                 for (int k = 0; k < RC; ++k) {
-                    const float total = split_sum(acc[k], nsplit);
+                    const float total = split_sum(sums[k], nsplit);
                     if (s == 0 && p0 + k < P) yr[p0 + k] = total + skip * sx[c * cols + cg * RC + k];
                 }
             }
         };
-        for (int c = 0; c < nt; ++c) token(c);
-        if (next_nt > 0) {
-            put_dt(raw, next_nt, there);
-            copies_wait();
+        if (nt == kChunk) {
+            // A full chunk unrolled: the column sums of its tokens wait in registers and are reduced over
+            // the lanes together after the loop, as independent shuffles instead of a chain per token.
+            float sums[kChunk][RC];
+#pragma unroll
+            for (int c = 0; c < kChunk; ++c) advance(c, sums[c]);
+#pragma unroll
+            for (int c = 0; c < kChunk; ++c) finish(c, sums[c]);
+        } else {
+            for (int c = 0; c < nt; ++c) {
+                float sums[RC];
+                advance(c, sums);
+                finish(c, sums);
+            }
         }
+        if (next_nt > 0) copies_wait();
         __syncthreads();
     }
 #pragma unroll
@@ -722,15 +736,17 @@ extern "C" int se_causal_conv(const void* x, int pitch, int c0, const float* w, 
     SE_LAUNCH_CHECK();
 }
 
+// steps: workspace of 2 * tokens * H floats (step sizes and decays), or null (then the kernel with one
+// column per thread computes them itself)
 extern "C" int se_ssm_scan(const float* xbc, const void* proj, int pitch, int dt_off, const float* dt_bias,
                            const float* a_log, const float* d_skip, float* state, long long state_pitch, const int* cu_q,
-                           const int* seq_rows, float* y, int entries, int H, int P, int N, int G, int dtype,
-                           cudaStream_t stream) {
+                           const int* seq_rows, float* y, float* steps, int tokens, int entries, int H, int P, int N, int G,
+                           int dtype, cudaStream_t stream) {
     if (entries <= 0) return 0;
     if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G) return SE_ERR_ARGUMENT;
     if (N > se::kMaxStateRows || H > 65535) return SE_ERR_UNSUPPORTED;
     int regs, nsplit, cols;
-    if (N <= se::kTileRows * 32) {
+    if (N <= se::kTileRows * 32 && steps != nullptr) {
         se::tile_plan(N, P, entries * H, &nsplit, &cols);
         const dim3 grid(entries, H, se::ceil_div(P, cols));
         const size_t smem = (size_t)2 * se::kChunk * (2 * nsplit * se::kTilePad + cols + 2) * sizeof(float);
@@ -739,9 +755,10 @@ extern "C" int se_ssm_scan(const float* xbc, const void* proj, int pitch, int dt
                 cudaError_t e = cudaFuncSetAttribute(se::ssm_scan_tile_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
                 if (e != cudaSuccess) return (int)e;
             }
+            se::ssm_steps_kernel<T><<<se::ceil_div(tokens * H, 256), 256, 0, stream>>>((const T*)proj, pitch, dt_off, dt_bias, a_log,
+                                                                                     steps, tokens, H);
             se::ssm_scan_tile_kernel<T><<<grid, nsplit * cols / se::kTileCols, smem, stream>>>(
-                xbc, (const T*)proj, pitch, dt_off, dt_bias, a_log, d_skip, state, state_pitch, cu_q, seq_rows, y, H, P, N, G,
-                nsplit, cols);
+                xbc, steps, d_skip, state, state_pitch, cu_q, seq_rows, y, H, P, N, G, nsplit, cols);
         });
         SE_LAUNCH_CHECK();
     }
