@@ -256,6 +256,13 @@ def activation_(x, kind: str):
     return x
 
 
+def softcap_(x, cap: float):
+    """x <- cap * tanh(x / cap) in place (32-bit arithmetic, rounded once)."""
+    _check(_fn("se_softcap", "pl" "f" "ip")(_ptr(x, None, "x"), x.numel(), float(cap), dtype_code(x.dtype), _stream()),
+           "softcap")
+    return x
+
+
 # ---- mixers with a recurrent state (csrc/recurrent.cu) -------------------------------------------
 
 def causal_conv(x, c0: int, w, bias, state, conv_off: int, step, out):

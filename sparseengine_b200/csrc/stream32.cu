@@ -114,7 +114,23 @@ __global__ void activation_kernel(T* x, size_t n, int kind) {
     for (size_t i = i0; i < n; i += stride) x[i] = from_float<T>(act_apply(to_float(x[i]), kind));
 }
 
+// x <- cap * tanh(x / cap) in place (32-bit arithmetic, rounded once): the cap on a model's logits
+template <typename T>
+__global__ void softcap_kernel(T* x, size_t n, float cap) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+        x[i] = from_float<T>(cap * tanhf(to_float(x[i]) / cap));
+}
+
 }  // namespace se
+
+extern "C" int se_softcap(void* x, long long n, float cap, int dtype, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (!(cap > 0.f)) return SE_ERR_ARGUMENT;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    SE_DISPATCH_DTYPE(dtype, T, se::softcap_kernel<T><<<blocks, 256, 0, stream>>>((T*)x, (size_t)n, cap));
+    SE_LAUNCH_CHECK();
+}
 
 extern "C" int se_embed_stream(const void* table, const int* ids, float* stream, void* act, int tokens, int hidden,
                                int vocab, float scale, int dtype, cudaStream_t stream_) {

@@ -207,6 +207,5 @@ class Model:
                 h, _ = self.final_norm.forward(h)
         logits = linear(h, self.head)
         if s.logit_softcap is not None:
-            c = float(s.logit_softcap)
-            logits = (torch.tanh(logits.float() / c) * c).to(logits.dtype)
+            ops.softcap_(logits, float(s.logit_softcap))
         return logits
