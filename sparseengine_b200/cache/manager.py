@@ -53,7 +53,9 @@ class CacheGroup:
         self.storage = None
         self.table = None
         if allocate:
-            if request.value_dim == request.head_dim:
+            if getattr(request, "layout", "kv") == "latent":      # one row per position
+                self.storage = torch.zeros(cache_layers, num_pages, page_size, request.head_dim, dtype=dtype, device=device)
+            elif request.value_dim == request.head_dim:
                 self.storage = torch.zeros(cache_layers, num_pages, 2, request.num_kv_heads, page_size,
                                            request.head_dim, dtype=dtype, device=device)
             else:       # per page the keys [kv head][slot][head_dim], then the values [kv head][slot][v_head_dim]

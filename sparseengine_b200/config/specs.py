@@ -136,6 +136,47 @@ class GatedDeltaSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Softmax attention whose keys and values are up-projections of one cached latent per position.
+
+    Queries go through a latent of their own (``q_rank``, RMS-normed); a head's query and key have
+    ``head_dim`` unrotated dims followed by ``rot_dim`` rotated ones.  The key/value projection gives
+    ``kv_rank`` latent dims (RMS-normed) plus ``rot_dim`` dims that form the rotated key part of every
+    head; unrotated keys and values are ``W_uk c`` and ``W_uv c``.  Only the latent and the rotated key
+    part are cached.  ``window``: keys p-window+1..p (None: all).  ``sink``: a learned logit per head
+    that joins the softmax's denominator, unscaled, with no key or value."""
+    kind: str = "latent_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0                 # unrotated dims of a head's query and key
+    rot_dim: int = 0                  # rotated dims of a head's query; the shared key part
+    v_head_dim: int = 0
+    q_rank: int = 0
+    kv_rank: int = 0
+    scale: float = 1.0
+    window: Optional[int] = None
+    sink: bool = False
+    position: Optional[Any] = None    # RotarySpec over (at most) rot_dim dims, split-half pairing
+    norm_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with one fixed decay per head: ``S <- decay S + k v^T``, ``o = S^T q``, no
+    softmax or denominator.  q and k are rotated (``position``), k is scaled by ``head_dim ** -0.5``
+    after the rotation; each head's ``o`` is divided by its root mean square (no weight), multiplied
+    by ``silu(gate)`` and projected."""
+    kind: str = "retention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    v_head_dim: int = 0
+    decays: tuple = ()                # one per head
+    position: Optional[Any] = None    # RotarySpec, split-half pairing
+    norm_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
 class MoESpec:
     """Routed SwiGLU experts."""
     kind: str = "moe"
@@ -143,8 +184,10 @@ class MoESpec:
     num_experts: int = 0
     top_k: int = 0
     intermediate_size: int = 0
-    score_fn: str = "sigmoid"         # "sigmoid" | "softmax"
-    selection_bias: bool = True       # bias added for selection only
+    # "sigmoid" | "softmax": scores over all experts.  "top_softmax": the bias is part of the logit, the
+    # largest logits are chosen and their weights are the softmax among the chosen logits.
+    score_fn: str = "sigmoid"
+    selection_bias: bool = True       # bias added for selection only ("top_softmax": part of the logit)
     renormalize: bool = True
     routed_scale: float = 1.0
     activation: str = "silu"
@@ -182,6 +225,8 @@ class LayerSpec:
     mixer_norm: Any
     feed_forward_norm: Any
     arrangement: str = "pre_norm"
+    # "pre_norm_stream": x <- x + mixer(norm(x)), x <- x + ff(norm(x)) over a 32-bit stream; the
+    # feed-forward (with its norm) may be None.
     # "post_norm": x <- norm(residual_scale * x + sublayer(x)) for each sublayer; the feed-forward
     # (with its norm) may be None
     residual_scale: float = 1.0
@@ -203,6 +248,10 @@ class ScheduleEntry:
     layer: int
     cache: Optional[int] = None
     write_cache: bool = True
+    # Before this visit the stream becomes W [x; x0], x0 being the embedding output and W the
+    # model's ``reinject_source`` tensor [width, 2 width] (a looped stack takes the embedding in
+    # again at the start of every pass).
+    reinject: bool = False
 
 
 @dataclass(frozen=True)
@@ -227,3 +276,4 @@ class ModelSpec:
     # stream is 32-bit whatever the activation type; blocks carry (its copy in the activation type,
     # the stream), the embedding is scaled in 32-bit and the final norm reads the stream.
     residual_stream: str = "activation"
+    reinject_source: Optional[str] = None           # checkpoint name of the [width, 2 width] matrix of ScheduleEntry.reinject

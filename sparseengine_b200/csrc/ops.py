@@ -47,6 +47,8 @@ LIMITS = {
     "attention_max_head_dim": 256,          # in steps of 16
     "layernorm_max_width": 51200,           # as the RMS norm: the row is kept in shared memory in 32-bit
     "recurrent_max_state_rows": 512,        # rows of a recurrence's state on the key/state side (16 registers x 32 lanes)
+    "latent_max_row": 640,                  # latent plus shared key part of one position (20 registers x 32 lanes)
+    "retention_max_head_dim": 256,          # rows of a retention state (32 registers x 8 warps)
     "grid_dim_yz": 65535,                   # heads, KV heads and a step's entries map to grid dimensions y and z
 }
 
@@ -263,6 +265,84 @@ def softcap_(x, cap: float):
     return x
 
 
+def add_rmsnorm_stream(x, y, w, eps: float, out32=None, out_act=None):
+    """A pre-norm model's 32-bit stream: ``v = x + y`` (``y`` optional, activation type) goes to
+    ``out32`` (which may be ``x``); ``out_act`` receives ``v / sqrt(mean(v^2) + eps) * w``, or, without
+    a weight, ``v`` rounded to the activation type."""
+    rows, hidden = x.shape
+    dt = out_act.dtype if out_act is not None else (y.dtype if y is not None else torch.float32)
+    if w is not None and w.shape != (hidden,):
+        raise ValueError(f"norm weight shape {tuple(w.shape)} does not match width {hidden}")
+    _check(_fn("se_add_rmsnorm_stream", "ppppp" "ii" "f" "ip")(
+        _ptr(x, torch.float32, "x"), _ptr(y, dt, "y"), _ptr(w, dt, "w"), _ptr(out32, torch.float32, "out32"),
+        _ptr(out_act, dt, "out_act"), rows, hidden, float(eps), dtype_code(dt), _stream()), "add_rmsnorm_stream")
+
+
+# ---- attention over a cached latent (csrc/latent_attention.cu) -----------------------------------
+
+def latent_prep(proj, q_w, kv_w, inv_freq, positions, token_seq, seq_rows, table, cache, cq_out, *, q_rank, rank, rot,
+                rotary_dim, eps, page_size, write_cache=True, num_pages=None):
+    """From a step's rows ``[q latent | kv latent | shared key part]``: the normalised query latent
+    (``cq_out``), and into each token's page slot the normalised kv latent and the rotated key part."""
+    tokens = proj.shape[0]
+    dt = proj.dtype
+    if proj.dim() != 2 or proj.stride(1) != 1 or proj.shape[1] != q_rank + rank + rot:
+        raise ValueError("proj must be [tokens, q_rank + rank + rot] with contiguous rows")
+    _check(_fn("se_latent_prep", "pippp" "ppp" "pi" "pp" "iiiii" "f" "iii" "p" "ip")(
+        proj.data_ptr(), proj.stride(0), _ptr(q_w, dt, "q_norm"), _ptr(kv_w, dt, "kv_norm"),
+        _ptr(inv_freq, torch.float32, "inv_freq"), _ptr(positions, torch.int32, "positions"),
+        _ptr(token_seq, torch.int32, "token_seq"), _ptr(seq_rows, torch.int32, "seq_rows"),
+        _ptr(table, torch.int32, "table"), table.shape[1], _ptr(cache, dt, "cache"), _ptr(cq_out, dt, "cq_out"),
+        tokens, q_rank, rank, rot, rotary_dim, float(eps), page_size,
+        cache.shape[0] if num_pages is None else int(num_pages), int(bool(write_cache)), _ptr(error_word(proj.device)),
+        dtype_code(dt), _stream()), "latent_prep")
+    return cq_out
+
+
+def latent_attention_plain(q_lat, q, inv_freq, cache, table, seq_rows, token_seq, positions, sink, out, *, heads,
+                           head_dim, rank, rot, rotary_dim, page_size, scale, window=None, num_pages=None):
+    """``q_lat`` float32 [heads, tokens, rank] (queries taken into the latent's space), ``q`` [tokens,
+    heads * (head_dim + rot)] whose rotated parts are rotated here; ``out`` [heads, tokens, rank]."""
+    tokens = q.shape[0]
+    dt = q.dtype
+    _check(_fn("se_latent_attention_plain", "ppipi" "ppi" "pppp" "p" "iiii" "i" "f" "ii" "p" "ip")(
+        _ptr(q_lat, torch.float32, "q_lat"), _ptr(q, None, "q"), head_dim, _ptr(inv_freq, torch.float32, "inv_freq"),
+        rotary_dim, _ptr(cache, dt, "cache"), _ptr(table, torch.int32, "table"), table.shape[1],
+        _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(token_seq, torch.int32, "token_seq"),
+        _ptr(positions, torch.int32, "positions"), _ptr(sink, torch.float32, "sink"), _ptr(out, dt, "out"),
+        tokens, heads, rank, rot, page_size, float(scale), int(window or 0),
+        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(q.device)), dtype_code(dt), _stream()),
+        "latent_attention_plain")
+    return out
+
+
+# ---- retention (csrc/retention.cu) ----------------------------------------------------------------
+
+def retention_prep(proj, q_off: int, k_off: int, inv_freq, positions, q32, k32, *, heads, head_dim, rotary_dim, k_scale):
+    tokens = proj.shape[0]
+    _check(_fn("se_retention_prep", "piii" "pp" "pp" "iiii" "f" "ip")(
+        proj.data_ptr(), proj.stride(0), int(q_off), int(k_off), _ptr(inv_freq, torch.float32, "inv_freq"),
+        _ptr(positions, torch.int32, "positions"), _ptr(q32, torch.float32, "q32"), _ptr(k32, torch.float32, "k32"),
+        tokens, heads, head_dim, rotary_dim, float(k_scale), dtype_code(proj.dtype), _stream()), "retention_prep")
+
+
+def retention_scan(q32, k32, proj, v_off: int, decay, state, step, o, *, heads, head_dim, v_head_dim):
+    _check(_fn("se_retention_scan", "pp" "pii" "p" "pl" "pp" "p" "iiii" "ip")(
+        _ptr(q32, torch.float32, "q32"), _ptr(k32, torch.float32, "k32"), proj.data_ptr(), proj.stride(0), int(v_off),
+        _ptr(decay, torch.float32, "decay"), _ptr(state, torch.float32, "state"), state.stride(0), _ptr(step.cu_q),
+        _ptr(step.seq_rows), _ptr(o, torch.float32, "o"), step.num_seqs, heads, head_dim, v_head_dim,
+        dtype_code(proj.dtype), _stream()), "retention_scan")
+    return o
+
+
+def retention_out(o, proj, g_off: int, out, *, heads, v_head_dim, eps):
+    tokens = proj.shape[0]
+    _check(_fn("se_retention_out", "ppii" "p" "iii" "f" "ip")(
+        _ptr(o, torch.float32, "o"), proj.data_ptr(), proj.stride(0), int(g_off), _ptr(out, proj.dtype, "out"), tokens,
+        heads, v_head_dim, float(eps), dtype_code(proj.dtype), _stream()), "retention_out")
+    return out
+
+
 # ---- mixers with a recurrent state (csrc/recurrent.cu) -------------------------------------------
 
 def causal_conv(x, c0: int, w, bias, state, conv_off: int, step, out):
@@ -326,7 +406,9 @@ def delta_out(o, gate, w, out, *, v_head_dim: int, eps: float):
 
 # ---- feed-forward ------------------------------------------------------------------------
 
-SCORE_FN = {"sigmoid": 0, "softmax": 1}
+# "top_softmax": the bias is part of the logit, the largest logits are chosen and weighed by a softmax
+# among themselves
+SCORE_FN = {"sigmoid": 0, "softmax": 1, "top_softmax": 2}
 
 
 def router(x, gate, bias, ids, weights, *, top_k, score_fn="sigmoid", renormalize=True, routed_scale=1.0,
@@ -430,7 +512,8 @@ _error_words = {}
 _WAIT_ROLES = "a tensor-core kernel timed out waiting on a barrier (role code {code}); its results are not valid"
 _INDEX_CODES = {21: "the q/k preparation kernel", 22: "the plain attention kernel", 23: "the split-key decode attention kernel",
                 24: "the prompt-portion attention kernel", 25: "the tcgen05 prompt-portion attention kernel",
-                26: "the block-table update kernel"}
+                26: "the block-table update kernel", 27: "the latent preparation kernel",
+                28: "the latent attention kernel", 29: "the tiled latent attention kernel"}
 
 
 def error_text(code: int) -> str:

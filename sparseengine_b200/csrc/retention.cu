@@ -1,0 +1,188 @@
+// Retention: linear attention with one fixed decay per head and no softmax or denominator.
+//
+//     S_t = decay[h] S_(t-1) + k_t v_t^T        (state [d, dv] per request and head, 32-bit)
+//     o_t = S_t^T q_t
+//
+// q and k are rotated by their position on the first `rotary_dim` dims of each head (dim i pairs
+// with i + rotary_dim/2, angle = position * inv_freq[i]); k is multiplied by `k_scale` after the
+// rotation.  Each head's o is divided by its root mean square and multiplied by silu(gate).
+// Rotation, scaling, state, sums and the norm are 32-bit; q, k, v and the gate come from the
+// projection in the activation type.
+//
+// A step brings any mix of prompt portions and single tokens: entry s owns the tokens
+// cu_q[s] .. cu_q[s+1]-1 and the state row seq_rows[s].
+#include "common.cuh"
+
+namespace se {
+
+// q32, k32 [tokens, heads, d]: rotated (k also scaled), 32-bit.  One thread per (token, head, dim).
+template <typename T>
+__global__ void retention_prep_kernel(const T* proj, int proj_stride, int q_off, int k_off,
+                                      const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                      float* __restrict__ q32, float* __restrict__ k32, int tokens, int heads, int d,
+                                      int rotary_dim, float k_scale) {
+    const size_t n = (size_t)tokens * heads * d;
+    const int half = rotary_dim / 2;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+        const int i = (int)(idx % d);
+        const int h = (int)((idx / d) % heads);
+        const int t = (int)(idx / ((size_t)d * heads));
+        const T* qp = proj + (size_t)t * proj_stride + q_off + h * d;
+        const T* kp = proj + (size_t)t * proj_stride + k_off + h * d;
+        float qv = to_float(qp[i]), kv = to_float(kp[i]);
+        if (i < rotary_dim) {
+            const int j = i < half ? i : i - half;
+            float sn, cs;
+            sincosf((float)positions[t] * inv_freq[j], &sn, &cs);
+            const float qu = to_float(qp[j]), qw = to_float(qp[j + half]);
+            const float ku = to_float(kp[j]), kw = to_float(kp[j + half]);
+            qv = i < half ? qu * cs - qw * sn : qw * cs + qu * sn;
+            kv = i < half ? ku * cs - kw * sn : kw * cs + ku * sn;
+        }
+        q32[idx] = qv;
+        k32[idx] = kv * k_scale;
+    }
+}
+
+constexpr int kRetWarps = 8;        // the state's rows are dealt to the warps: warp r holds rows r, r + 8, ...
+constexpr int kRetTokens = 8;       // tokens staged at a time
+
+// One block per (entry, head, 32 value columns).  Thread (warp r, lane c) keeps rows r + 8 n of column
+// c in registers; a token's partial sums over a warp's rows meet in shared memory, eight tokens at
+// a time.  Sums run in one fixed order whatever the batch or the portion.
+template <typename T, int NPT>
+__global__ void __launch_bounds__(32 * kRetWarps)
+retention_scan_kernel(const float* __restrict__ q32, const float* __restrict__ k32, const T* proj, int proj_stride,
+                      int v_off, const float* __restrict__ decay, float* state, long long state_stride,
+                      const int* __restrict__ cu_q, const int* __restrict__ seq_rows, float* __restrict__ o, int heads,
+                      int d, int dv) {
+    extern __shared__ float ret_smem[];
+    float* qs = ret_smem;                                   // [kRetTokens][d]
+    float* ks = qs + kRetTokens * d;                        // [kRetTokens][d]
+    float* vs = ks + kRetTokens * d;                        // [kRetTokens][32]
+    float* red = vs + kRetTokens * 32;                      // [kRetTokens][kRetWarps][32]
+    const int s = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col = c0 + lane;
+    const bool col_ok = col < dv;
+    const int t0 = cu_q[s], t1 = cu_q[s + 1];
+    if (t1 <= t0) return;
+    const float g = decay[h];
+    float* S = state + (size_t)seq_rows[s] * state_stride + (size_t)h * d * dv;
+    float st[NPT];
+#pragma unroll
+    for (int n = 0; n < NPT; ++n) {
+        const int i = warp + kRetWarps * n;
+        st[n] = (i < d && col_ok) ? S[(size_t)i * dv + col] : 0.f;
+    }
+    for (int tb = t0; tb < t1; tb += kRetTokens) {
+        const int nt = min(kRetTokens, t1 - tb);
+        __syncthreads();                                    // the last round's sums have been read
+        for (int x = threadIdx.x; x < nt * d; x += blockDim.x) {
+            const int tt = x / d, i = x - tt * d;
+            const size_t at = ((size_t)(tb + tt) * heads + h) * d + i;
+            qs[tt * d + i] = q32[at];
+            ks[tt * d + i] = k32[at];
+        }
+        for (int x = threadIdx.x; x < nt * 32; x += blockDim.x) {
+            const int tt = x >> 5, c = x & 31;
+            vs[x] = c0 + c < dv ? to_float(proj[(size_t)(tb + tt) * proj_stride + v_off + h * dv + c0 + c]) : 0.f;
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float v = vs[tt * 32 + lane];
+            float acc = 0.f;
+#pragma unroll
+            for (int n = 0; n < NPT; ++n) {
+                const int i = warp + kRetWarps * n;
+                if (i < d) {
+                    st[n] = g * st[n] + ks[tt * d + i] * v;
+                    acc += st[n] * qs[tt * d + i];
+                }
+            }
+            red[(tt * kRetWarps + warp) * 32 + lane] = acc;
+        }
+        __syncthreads();
+        for (int x = threadIdx.x; x < nt * 32; x += blockDim.x) {
+            const int tt = x >> 5, c = x & 31;
+            if (c0 + c < dv) {
+                float sum = 0.f;
+#pragma unroll
+                for (int w = 0; w < kRetWarps; ++w) sum += red[(tt * kRetWarps + w) * 32 + c];
+                o[((size_t)(tb + tt) * heads + h) * dv + c0 + c] = sum;
+            }
+        }
+    }
+#pragma unroll
+    for (int n = 0; n < NPT; ++n) {
+        const int i = warp + kRetWarps * n;
+        if (i < d && col_ok) S[(size_t)i * dv + col] = st[n];
+    }
+}
+
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]); a warp per (token, head).
+template <typename T>
+__global__ void retention_out_kernel(const float* __restrict__ o, const T* proj, int proj_stride, int g_off,
+                                     T* __restrict__ out, int rows, int heads, int dv, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const int t = r / heads, h = r - t * heads;
+    const float* op = o + (size_t)r * dv;
+    float ss = 0.f;
+    for (int i = lane; i < dv; i += 32) ss += op[i] * op[i];
+    const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+    const T* gp = proj + (size_t)t * proj_stride + g_off + h * dv;
+    for (int i = lane; i < dv; i += 32) {
+        const float gv = to_float(gp[i]);
+        out[(size_t)r * dv + i] = from_float<T>(op[i] * inv * (gv / (1.f + expf(-gv))));
+    }
+}
+
+}  // namespace se
+
+extern "C" int se_retention_max_head_dim() { return se::kRetWarps * 32; }
+
+extern "C" int se_retention_prep(const void* proj, int proj_stride, int q_off, int k_off, const float* inv_freq,
+                                 const int* positions, float* q32, float* k32, int tokens, int heads, int d,
+                                 int rotary_dim, float k_scale, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (heads <= 0 || d <= 0 || rotary_dim < 0 || rotary_dim > d || (rotary_dim & 1)) return SE_ERR_ARGUMENT;
+    const long long n = (long long)tokens * heads * d;
+    const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::retention_prep_kernel<T><<<blocks, 256, 0, stream>>>((const T*)proj, proj_stride, q_off, k_off, inv_freq,
+                                                                  positions, q32, k32, tokens, heads, d, rotary_dim, k_scale));
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_retention_scan(const float* q32, const float* k32, const void* proj, int proj_stride, int v_off,
+                                 const float* decay, float* state, long long state_stride, const int* cu_q,
+                                 const int* seq_rows, float* o, int entries, int heads, int d, int dv, int dtype,
+                                 cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (d <= 0 || d > se_retention_max_head_dim() || dv <= 0 || heads <= 0 || heads > 65535 || (dv + 31) / 32 > 65535)
+        return SE_ERR_UNSUPPORTED;
+    dim3 grid(entries, heads, (dv + 31) / 32);
+    const size_t smem = (size_t)(2 * se::kRetTokens * d + se::kRetTokens * 32 + se::kRetTokens * se::kRetWarps * 32) * sizeof(float);
+#define SE_RET_LAUNCH(NPT)                                                                                          \
+    se::retention_scan_kernel<T, NPT><<<grid, 32 * se::kRetWarps, smem, stream>>>(                                  \
+        q32, k32, (const T*)proj, proj_stride, v_off, decay, state, state_stride, cu_q, seq_rows, o, heads, d, dv)
+    SE_DISPATCH_DTYPE(dtype, T, {
+        if (d <= 8 * se::kRetWarps) SE_RET_LAUNCH(8);
+        else if (d <= 16 * se::kRetWarps) SE_RET_LAUNCH(16);
+        else SE_RET_LAUNCH(32);
+    });
+#undef SE_RET_LAUNCH
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_retention_out(const float* o, const void* proj, int proj_stride, int g_off, void* out, int tokens,
+                                int heads, int dv, float eps, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const int rows = tokens * heads;
+    SE_DISPATCH_DTYPE(dtype, T,
+        se::retention_out_kernel<T><<<(rows + 7) / 8, 256, 0, stream>>>(o, (const T*)proj, proj_stride, g_off, (T*)out,
+                                                                         rows, heads, dv, eps));
+    SE_LAUNCH_CHECK();
+}

@@ -384,6 +384,12 @@ __global__ void router_select_kernel(const LogitParts src, const float* __restri
             pj[e] = pe;
             sj[e] = (s == s) ? s : INFINITY;
         }
+    } else if (score_fn == 2) {   // the bias is part of the logit; the chosen logits are weighed by a softmax among themselves (below)
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+            const float s = lg[e] + (bias ? bias[e] : 0.f);
+            pj[e] = s;
+            sj[e] = (s == s) ? s : INFINITY;
+        }
     } else {
         for (int e = threadIdx.x; e < experts; e += blockDim.x) {     // logit and bias: one trip to memory
             const float l = lg[e], bv = bias ? bias[e] : 0.f;
@@ -449,6 +455,13 @@ __global__ void router_select_kernel(const LogitParts src, const float* __restri
     }
     // every writer adds the chosen probabilities in slot order, as one thread would
     for (int k = threadIdx.x; k < top_k; k += blockDim.x) {
+        if (score_fn == 2) {          // softmax over the chosen logits only
+            float mx = -INFINITY, sum = 0.f;
+            for (int s = 0; s < top_k; ++s) mx = fmaxf(mx, w_s[s]);
+            for (int s = 0; s < top_k; ++s) sum += expf(w_s[s] - mx);
+            weights[(size_t)t * top_k + k] = expf(w_s[k] - mx) / sum * routed_scale;
+            continue;
+        }
         float sum = 0.f;
         for (int s = 0; s < top_k; ++s) sum += w_s[s];
         weights[(size_t)t * top_k + k] = (renormalize ? w_s[k] / sum : w_s[k]) * routed_scale;

@@ -87,6 +87,32 @@ __global__ void add_layernorm_kernel(const float* x, const T* y, float alpha, co
     }
 }
 
+// One block per row of a pre-norm model's 32-bit stream.  v = x + y (y optional) goes to out32
+// (which may be x itself); with a weight, out_act = v / sqrt(mean(v^2) + eps) * w, without one
+// out_act = v rounded (both optional).
+template <typename T>
+__global__ void add_rmsnorm_stream_kernel(const float* x, const T* y, const T* __restrict__ w, float* out32, T* out_act,
+                                          int hidden, float eps) {
+    extern __shared__ __align__(16) float row[];
+    __shared__ float scratch[33];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = x[base + i];
+        if (y != nullptr) v += to_float(y[base + i]);
+        row[i] = v;
+        ss += v * v;
+        if (out32 != nullptr) out32[base + i] = v;
+    }
+    if (out_act == nullptr) return;
+    if (w == nullptr) {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) out_act[base + i] = from_float<T>(row[i]);   // its own writes
+        return;
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out_act[base + i] = from_float<T>(row[i] * inv * to_float(w[i]));
+}
+
 __device__ __forceinline__ float act_apply(float v, int kind) {
     if (kind == 0) { const float r = fmaxf(v, 0.f); return r * r; }                       // squared relu
     if (kind == 1) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));   // gelu (tanh form)
@@ -156,6 +182,23 @@ extern "C" int se_add_layernorm(const float* x, const void* y, float alpha, cons
         cudaError_t e = SE_LAUNCH_DEPENDENT("norm", se::add_layernorm_kernel<T>, dim3(rows), dim3(threads), smem, stream, x,
                                              (const T*)y, alpha, (const T*)w, (const T*)b, out32, (T*)out_act, hidden, eps);
         if (e != cudaSuccess) return (int)e;
+    });
+    SE_LAUNCH_CHECK();
+}
+
+extern "C" int se_add_rmsnorm_stream(const float* x, const void* y, const void* w, float* out32, void* out_act, int rows,
+                                     int hidden, float eps, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (hidden <= 0 || hidden > se_layernorm_max_width()) return SE_ERR_UNSUPPORTED;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    const int threads = hidden >= 8192 ? 512 : hidden >= 1024 ? 256 : 128;
+    SE_DISPATCH_DTYPE(dtype, T, {
+        if (smem > 40 * 1024) {
+            cudaError_t e = cudaFuncSetAttribute(se::add_rmsnorm_stream_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        se::add_rmsnorm_stream_kernel<T><<<rows, threads, smem, stream>>>(x, (const T*)y, (const T*)w, out32, (T*)out_act,
+                                                                          hidden, eps);
     });
     SE_LAUNCH_CHECK();
 }

@@ -16,8 +16,8 @@ import torch
 from ..config.specs import ModelSpec, ParamSpec, Source
 from ..csrc import ops
 from ..parts.base import KVRequest, StateRequest, StepContext, make_norm
-from ..parts.block import PostNormBlock, PreNormBlock, make_block
-from ..parts.linear import linear
+from ..parts.block import PostNormBlock, PreNormBlock, PreNormStreamBlock, make_block
+from ..parts.linear import linear, linear32
 
 
 @dataclass
@@ -61,6 +61,16 @@ class Model:
         self.stream_taps = None  # a list: receives a copy of the residual stream after every schedule entry (a debugging aid)
         if spec.residual_stream not in ("activation", "float32"):
             raise ValueError(f"residual_stream {spec.residual_stream!r} is not known ('activation' or 'float32')")
+        # blocks over the 32-bit stream that carry (output not yet added, stream)
+        self.pending_stream = any(isinstance(b, PreNormStreamBlock) for b in self.blocks)
+        if self.pending_stream and not (all(isinstance(b, PreNormStreamBlock) for b in self.blocks)
+                                        and spec.residual_stream == "float32"
+                                        and hasattr(self.final_norm, "forward_stream")):
+            raise ValueError("pre_norm_stream blocks need residual_stream='float32', a final norm with forward_stream, "
+                             "and no other arrangement beside them")
+        self.reinject = None
+        if any(e.reinject for e in spec.order) and not (self.pending_stream and spec.reinject_source):
+            raise ValueError("ScheduleEntry.reinject needs pre_norm_stream blocks and ModelSpec.reinject_source")
         for i, e in enumerate(spec.order):
             if not 0 <= e.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {i} names layer {e.layer}, the model has {len(self.blocks)}")
@@ -75,6 +85,9 @@ class Model:
         if s.head_source is not None:
             out.append(Param(self, "head", "head", ParamSpec((s.vocab_size, s.hidden_size)),
                              (Source(s.head_source),)))
+        if s.reinject_source is not None:
+            out.append(Param(self, "reinject", "reinject", ParamSpec((s.hidden_size, 2 * s.hidden_size)),
+                             (Source(s.reinject_source),)))
         for name, p in self.final_norm.parameters().items():
             source = (s.final_norm_sources or {}).get(name, s.final_norm_source)
             out.append(Param(self.final_norm, name, f"final_norm.{name}", p, (Source(source),)))
@@ -101,6 +114,10 @@ class Model:
                 owner.bind(tensors)
         if self.spec.head_source is None:
             self.head = self.embed
+        if self.reinject is not None:       # W [x; x0] = W_x x + W_0 x0: the second term is the same for every pass of a step
+            width = self.spec.hidden_size
+            self._reinject_x = self.reinject[:, :width].contiguous()
+            self._reinject_0 = self.reinject[:, width:].contiguous()
 
     def param_dtype(self, p: ParamSpec) -> torch.dtype:
         return torch.float32 if p.dtype == "float32" else self.dtype
@@ -170,7 +187,17 @@ class Model:
         s = self.spec
         stream32 = s.residual_stream == "float32"
         hidden = torch.empty(step.num_tokens, s.hidden_size, dtype=self.dtype, device=step.token_ids.device)
-        if stream32:
+        pending_stream = self.pending_stream
+        x0 = x0_term = None
+        if pending_stream:
+            # (output not yet added, 32-bit stream); `hidden` keeps the embedding output for the re-injections
+            residual = torch.empty(hidden.shape, dtype=torch.float32, device=hidden.device)
+            ops.embed_stream(self.embed, step.token_ids, residual, hidden if self.dtype != torch.float32 else None,
+                             scale=s.embed_scale)
+            if self.reinject is not None:
+                x0 = hidden if self.dtype != torch.float32 else residual.clone()
+            hidden = None
+        elif stream32:
             # the stream is 32-bit whatever the activation type; `hidden` is its copy for the matrix products
             residual = hidden if self.dtype == torch.float32 else torch.empty(hidden.shape, dtype=torch.float32,
                                                                               device=hidden.device)
@@ -183,16 +210,35 @@ class Model:
             residual = None
         for entry, slot in zip(s.order, slots):
             block = self.blocks[entry.layer]
+            if entry.reinject:
+                # the stream becomes W_x x + W_0 x0 (32-bit sums; x rounded to the activation type for the product)
+                x = torch.empty(residual.shape, dtype=self.dtype, device=residual.device)
+                ops.add_rmsnorm_stream(residual, hidden, None, 0.0, out_act=x)
+                if x0_term is None:
+                    x0_term = linear32(x0, self._reinject_0)
+                residual = linear32(x, self._reinject_x).add_(x0_term)
+                hidden = None
             if self.profile is None:
                 hidden, residual = block.forward(hidden, residual, step, slot)
             else:
                 hidden, residual = self._timed_block(block, hidden, residual, step, slot)
             if self.stream_taps is not None:
-                self.stream_taps.append((residual if stream32 else hidden).float().clone())
+                tap = (residual if stream32 else hidden).float().clone()
+                if pending_stream and hidden is not None:
+                    tap += hidden.float()
+                self.stream_taps.append(tap)
         if want_rows is None or want_rows.numel() == 0:
             return None
         n = want_rows.numel()
-        if stream32:        # the final norm reads the wanted rows of the stream
+        if pending_stream:  # the wanted rows of the stream and of what it has not taken in yet
+            r = torch.empty(n, s.hidden_size, dtype=torch.float32, device=residual.device)
+            ops.gather_rows(residual, want_rows, r)
+            p = None
+            if hidden is not None:
+                p = torch.empty(n, s.hidden_size, dtype=self.dtype, device=residual.device)
+                ops.gather_rows(hidden, want_rows, p)
+            h, _ = self.final_norm.forward_stream(r, p)
+        elif stream32:      # the final norm reads the wanted rows of the stream
             r = torch.empty(n, s.hidden_size, dtype=torch.float32, device=hidden.device)
             ops.gather_rows(residual, want_rows, r)
             h, _ = self.final_norm.forward(r)

@@ -1,2 +1,2 @@
 """Architecture builders.  Importing this package registers them."""
-from . import bavutar, minimax_m2  # noqa: F401
+from . import bavutar, minimax_m2, zisevik  # noqa: F401

@@ -34,6 +34,9 @@ class KVRequest:
     head_dim: int
     window: Optional[int] = None     # None: every key is kept; n: only the last n
     v_head_dim: Optional[int] = None # the values' head size where it differs from head_dim
+    # "kv": keys and values per KV head.  "latent": one row of head_dim elements per position and
+    # nothing else (keys and values are derived from it); num_kv_heads is 1.
+    layout: str = "kv"
 
     @property
     def value_dim(self) -> int:
@@ -41,7 +44,9 @@ class KVRequest:
 
     @property
     def elems_per_token(self) -> int:
-        """Keys and values of one position in one cache layer."""
+        """What one position holds in one cache layer."""
+        if self.layout == "latent":
+            return self.head_dim
         return self.num_kv_heads * (self.head_dim + self.value_dim)
 
 
@@ -55,7 +60,8 @@ class StateRequest:
 class LayerSlot:
     """What one visit of the execution order may touch besides its weights."""
     # [pages, 2, kv heads, page_size, head_dim] of its cache layer; with values of another head size
-    # [pages, kv heads * page_size * (head_dim + v_head_dim)]: per page the keys, then the values
+    # [pages, kv heads * page_size * (head_dim + v_head_dim)]: per page the keys, then the values;
+    # a latent layout: [pages, page_size, head_dim]
     kv: Optional[torch.Tensor] = None
     table: Optional[torch.Tensor] = None     # [rows, max pages] int32 block table of its group
     page_size: int = 0

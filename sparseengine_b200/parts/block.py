@@ -10,7 +10,8 @@ the one that may ask for pages or state), ``forward(hidden, residual, step, slot
 ``(hidden, residual)``, and an attribute ``mixer``.  Parts beyond the four of ``pre_norm`` come
 from ``LayerSpec.extra``.
 
-``post_norm`` is the second built-in arrangement (:class:`PostNormBlock`).
+``post_norm`` (:class:`PostNormBlock`) and ``pre_norm_stream`` (:class:`PreNormStreamBlock`) are the
+arrangements over a 32-bit stream.
 """
 from __future__ import annotations
 
@@ -76,7 +77,44 @@ class PostNormBlock:
         return hidden, stream
 
 
-ARRANGEMENTS = {"pre_norm": PreNormBlock, "post_norm": PostNormBlock}
+class PreNormStreamBlock:
+    """Norm before each sublayer, over a 32-bit stream: ``x <- x + mixer(norm(x))``, then (if the layer
+    has a feed-forward) ``x <- x + feed_forward(norm(x))``.  The block carries ``(pending, stream)``:
+    ``pending`` is the last sublayer's output that the stream has not taken in yet (None at the
+    start); the next norm call adds it in 32-bit and normalises the sum in one kernel.  Whoever
+    needs the stream itself (the model's last norm, a tap, the start of a looped pass) adds
+    ``pending`` first.  The norms are parts with ``forward_stream(stream, y)``
+    (``parts.norm.RMSNorm``)."""
+
+    def __init__(self, spec, dtype):
+        self.spec = spec
+        self.mixer = make_mixer(spec.mixer, dtype)
+        self.mixer_norm = make_norm(spec.mixer_norm, dtype)
+        self.feed_forward = self.feed_forward_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = make_feed_forward(spec.feed_forward, dtype)
+            self.feed_forward_norm = make_norm(spec.feed_forward_norm, dtype)
+        for n in (self.mixer_norm, self.feed_forward_norm):
+            if n is not None and not hasattr(n, "forward_stream"):
+                raise ValueError("a block over the 32-bit stream needs norms with forward_stream")
+
+    def parts(self) -> dict:
+        out = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
+        if self.feed_forward is not None:
+            out["feed_forward"] = self.feed_forward
+            out["feed_forward_norm"] = self.feed_forward_norm
+        return out
+
+    def forward(self, pending, stream, step, slot):
+        x, stream = self.mixer_norm.forward_stream(stream, pending)
+        pending = self.mixer.forward(x, step, slot)
+        if self.feed_forward is not None:
+            x, stream = self.feed_forward_norm.forward_stream(stream, pending)
+            pending = self.feed_forward.forward(x, step)
+        return pending, stream
+
+
+ARRANGEMENTS = {"pre_norm": PreNormBlock, "post_norm": PostNormBlock, "pre_norm_stream": PreNormStreamBlock}
 
 
 def make_block(spec, dtype):

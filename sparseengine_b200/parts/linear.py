@@ -47,3 +47,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor | None = None) ->
     if out is None:
         return torch.matmul(x, w.t())
     return torch.matmul(x, w.t(), out=out)
+
+
+def linear32(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """x [rows, in] . w [out, in]^T with the result left in 32-bit (not rounded to the activation type):
+    a product whose output joins a 32-bit residual stream."""
+    if x.dtype != w.dtype:
+        raise TypeError(f"linear32: activation {x.dtype} and weight {w.dtype} differ")
+    if x.dtype == torch.float32:
+        return torch.matmul(x, w.t())
+    return torch.mm(x, w.t(), out_dtype=torch.float32)

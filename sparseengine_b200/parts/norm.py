@@ -34,6 +34,14 @@ class RMSNorm(Norm):
         ops.rmsnorm(x, self.weight, self.spec.eps, out, residual=residual, residual_out=new_residual)
         return out, new_residual
 
+    def forward_stream(self, stream, y=None):
+        """Over a 32-bit residual stream (kernel: csrc/stream32.cu): ``stream += y`` in place (``y``:
+        the last sublayer's output in the activation type, or None), then the norm of the sum in the
+        activation type.  Returns ``(normed, stream)``."""
+        out = torch.empty(stream.shape, dtype=self.dtype, device=stream.device)
+        ops.add_rmsnorm_stream(stream, y, self.weight, self.spec.eps, out32=stream if y is not None else None, out_act=out)
+        return out, stream
+
 
 register_norm("rms", RMSNorm)
 

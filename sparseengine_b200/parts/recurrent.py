@@ -14,8 +14,9 @@ import torch
 
 from ..config.specs import ParamSpec
 from ..csrc import ops
-from .base import Mixer, StateRequest, register_mixer
+from .base import Mixer, StateRequest, make_position, register_mixer
 from .linear import linear
+from .position import as_rotary_args
 
 
 def _check_state_rows(rows: int, what: str) -> None:
@@ -137,5 +138,68 @@ class GatedDeltaMixer(Mixer):
         return linear(out, self.o)
 
 
+class RetentionMixer(Mixer):
+    """``[q | k | v | g] = in_proj(h)``; q and k rotated by position, k times ``head_dim ** -0.5``; per
+    head ``S <- decay S + k v^T``, ``o = S^T q`` with a fixed decay; each head's ``o`` over its root
+    mean square, times ``silu(g)``; out projection (kernels: csrc/retention.cu).  The state is one
+    32-bit ``[heads, head_dim, v_head_dim]`` row per request."""
+    graph_safe = True
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        s = spec
+        if min(s.num_heads, s.head_dim, s.v_head_dim, s.hidden_size) <= 0:
+            raise ValueError("the sizes of a retention mixer must be positive")
+        if len(s.decays) != s.num_heads:
+            raise ValueError(f"a retention mixer needs one decay per head ({s.num_heads}), got {len(s.decays)}")
+        if s.head_dim > ops.LIMITS["retention_max_head_dim"]:
+            raise ValueError(f"head_dim {s.head_dim} is not supported (at most {ops.LIMITS['retention_max_head_dim']}: "
+                             "a state column's rows live in the registers of eight warps)")
+        if s.num_heads > ops.LIMITS["grid_dim_yz"]:
+            raise ValueError("heads are a grid dimension of the kernels (at most 65,535)")
+        self.position = make_position(s.position, dtype) if s.position is not None else None
+        if self.position is not None:
+            if s.position.pairing != "split_half":
+                raise ValueError("the retention kernels rotate split halves only")
+            if s.position.rotary_dim > s.head_dim:
+                raise ValueError(f"the position encoding rotates {s.position.rotary_dim} dims, a head has {s.head_dim}")
+        self.qk = s.num_heads * s.head_dim
+        self.vv = s.num_heads * s.v_head_dim
+        self._decay = None
+
+    def parameters(self):
+        s = self.spec
+        return {"in_proj": ParamSpec((2 * self.qk + 2 * self.vv, s.hidden_size)),
+                "o": ParamSpec((s.hidden_size, self.vv))}
+
+    def state_request(self):
+        s = self.spec
+        return StateRequest((s.num_heads * s.head_dim * s.v_head_dim,), torch.float32)
+
+    def forward(self, x, step, slot):
+        s = self.spec
+        tokens, dev = x.shape[0], x.device
+        if self._decay is None or self._decay.device != dev:
+            self._decay = torch.tensor([float(g) for g in s.decays], dtype=torch.float32, device=dev)
+        inv_freq, rotary_dim = None, 0
+        if self.position is not None:
+            rope = as_rotary_args(self.position.kernel_args(dev))
+            if rope.scale != 1.0:
+                raise ValueError("the retention kernels take no factor on cos and sin")
+            inv_freq, rotary_dim = rope.inv_freq, rope.rotary_dim
+        proj = linear(x, self.in_proj)
+        q32 = torch.empty(tokens, self.qk, dtype=torch.float32, device=dev)
+        k32 = torch.empty(tokens, self.qk, dtype=torch.float32, device=dev)
+        ops.retention_prep(proj, 0, self.qk, inv_freq, step.positions, q32, k32, heads=s.num_heads, head_dim=s.head_dim,
+                           rotary_dim=rotary_dim, k_scale=s.head_dim ** -0.5)
+        o = torch.empty(tokens, self.vv, dtype=torch.float32, device=dev)
+        ops.retention_scan(q32, k32, proj, 2 * self.qk, self._decay, slot.state, step, o, heads=s.num_heads,
+                           head_dim=s.head_dim, v_head_dim=s.v_head_dim)
+        gated = torch.empty(tokens, self.vv, dtype=x.dtype, device=dev)
+        ops.retention_out(o, proj, 2 * self.qk + self.vv, gated, heads=s.num_heads, v_head_dim=s.v_head_dim, eps=s.norm_eps)
+        return linear(gated, self.o)
+
+
+register_mixer("retention", RetentionMixer)
 register_mixer("mamba2", StateSpaceMixer)
 register_mixer("channel_delta", GatedDeltaMixer)
