@@ -54,7 +54,9 @@ def latent_attention(h, w, p, m, eps):
     v = (c @ w[p + "uv"].T).view(T, H, dv)
     scores = (torch.einsum("ihd,jhd->hij", q_plain, k_plain) + torch.einsum("ihd,jd->hij", q_rot, k_rot)) * m["scale"]
     i, j = pos[:, None], pos[None, :]
-    seen = (i - j >= 0) & (i - j < m["mask"]["size"])
+    seen = i - j >= 0
+    if m.get("mask"):                                             # a sliding window; without one every earlier key is seen
+        seen = seen & (i - j < m["mask"]["size"])
     scores = scores.masked_fill(~seen[None], float("-inf"))
     sink = w[p + "sink"].to(F64)[:, None, None].expand(H, T, 1)
     both = torch.cat([scores, sink], -1)
@@ -137,3 +139,53 @@ def forward(config, weights, tokens, taps=None):
         if taps is not None:
             taps.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def tensor_shapes(config):
+    """Checkpoint tensor name -> shape, for a configuration dictionary."""
+    W = config["width"]
+    out = {"embed": (config["vocab"], W), "head": (config["vocab"], W), "final.norm": (W,)}
+    if config.get("loop"):
+        out["loop.in"] = (W, 2 * W)
+    for i, spec in enumerate(config["layers"]):
+        p, m = f"l{i}.", spec["mixer"]
+        out[p + "norm1"] = (W,)
+        H, d, dv = m["heads"], m["dim"], m["vdim"]
+        if spec["type"] == "retention":
+            out.update({p + "mix.q": (H * d, W), p + "mix.k": (H * d, W), p + "mix.v": (H * dv, W),
+                        p + "mix.g": (H * dv, W), p + "mix.o": (W, H * dv)})
+        else:
+            r, qr, kr = m["rot_dim"], m["q_rank"], m["kv_rank"]
+            out.update({p + "mix.dq": (qr, W), p + "mix.dq.norm": (qr,), p + "mix.uq": (H * (d + r), qr),
+                        p + "mix.dkv": (kr + r, W), p + "mix.dkv.norm": (kr,), p + "mix.uk": (H * d, kr),
+                        p + "mix.uv": (H * dv, kr), p + "mix.sink": (H,), p + "mix.o": (W, H * dv)})
+        mlp = spec.get("mlp")
+        if mlp is None:
+            continue
+        out[p + "norm2"] = (W,)
+        if mlp["kind"] == "dense":
+            out.update({p + "mlp.up": (mlp["ff"], W), p + "mlp.down": (W, mlp["ff"])})
+        else:
+            E, ff = mlp["router"]["experts"], mlp["expert"]["ff"]
+            out.update({p + "mlp.router": (E, W), p + "mlp.router.b": (E,)})
+            for e in range(E):
+                out.update({p + f"mlp.e{e}.gate": (ff, W), p + f"mlp.e{e}.up": (ff, W), p + f"mlp.e{e}.down": (W, ff)})
+    return out
+
+
+def random_weights(config, seed, gain=1.0):
+    """bfloat16 tensors of a size that keeps activations of order one."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(config).items():
+        x = torch.randn(shape, generator=g)
+        if name.endswith(("norm", "norm1", "norm2")):
+            t = 1.0 + 0.2 * x
+        elif name.endswith(("sink", "router.b")):
+            t = 0.7 * x
+        elif name == "embed":
+            t = x
+        else:
+            t = gain * x / math.sqrt(shape[-1])
+        out[name] = t.to(torch.bfloat16)
+    return out

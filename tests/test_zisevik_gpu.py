@@ -1,0 +1,367 @@
+"""The Zisevik design in the engine against the plain implementation (tests/plain_zisevik.py): each
+mechanism alone, whole prompts against token-by-token decoding, portions down to two tokens, mixed
+batches with pages and state slots that are used again, keys at the window's two edges and at page
+borders, the sink, a far token under a slow decay, the first tokens, long decoding, other sizes
+(also values equal to one another or to 1), and greedy generation through ``LLM``."""
+import copy
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_zisevik as pz
+import trace_util as tu
+
+pytestmark = pytest.mark.gpu
+
+
+def dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def moe(experts, top, ff):
+    return {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+
+
+def lat(heads, dim, rot_dim, vdim, q_rank, kv_rank, window, scale=None, base=10000.0, mlp=None):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "q_rank": q_rank, "kv_rank": kv_rank,
+         "scale": scale if scale is not None else (dim + rot_dim) ** -0.5, "rot": {"base": base, "dims": rot_dim}}
+    if window is not None:
+        m["mask"] = {"size": window}
+    return {"type": "latent_attention", "mixer": m, "mlp": mlp}
+
+
+def ret(heads, dim, vdim, decay, rot_dims=None, base=10000.0, mlp=None):
+    m = {"heads": heads, "dim": dim, "vdim": vdim, "decay": list(decay),
+         "rot": {"base": base, "dims": dim if rot_dims is None else rot_dims}}
+    return {"type": "retention", "mixer": m, "mlp": mlp}
+
+
+def config(width, vocab, layers, loop=None, eps=1e-6):
+    c = {"architecture": "Zisevik", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": eps}}
+    if loop is not None:
+        c["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return c
+
+
+CONFIGS = {
+    # both mixers and both feed-forwards; a rotation over part of a head; two windows (two page groups); a loop from layer 0
+    "hybrid": config(96, 160, [ret(4, 16, 24, (0.9, 0.97, 0.99, 0.999), rot_dims=8, mlp=dense(128)),
+                               lat(6, 16, 8, 12, 20, 24, 11, mlp=moe(5, 2, 24)),
+                               lat(3, 8, 16, 20, 12, 40, 7, base=500.0, mlp=dense(64))], loop=(0, 2, 2)),
+    # a loop in the middle, run three times; a layer without feed-forward; no window on one layer
+    "middle": config(64, 100, [lat(2, 16, 16, 16, 24, 32, None), ret(2, 32, 16, (0.95, 0.995), mlp=moe(4, 1, 32)),
+                               lat(2, 16, 16, 16, 24, 32, 20, mlp=dense(96)), ret(4, 8, 8, (0.5, 0.8, 0.9, 1.0))],
+                      loop=(1, 3, 3)),
+    # sizes that bfloat16 steps give to the tensor-core kernels (row pitches of 16 bytes); no loop
+    "wide": config(128, 200, [lat(4, 32, 32, 32, 64, 64, 33, mlp=moe(8, 2, 64)), ret(2, 64, 64, (0.98, 0.999), mlp=dense(256)),
+                              lat(4, 32, 32, 32, 64, 64, 33, mlp=moe(8, 3, 64))]),
+    # sizes that are equal or 1: one head, one expert, a window of one key, a loop of one pass
+    "ones": config(32, 48, [lat(1, 32, 32, 32, 32, 32, 1, mlp=moe(1, 1, 32)), ret(1, 32, 32, (0.9,), mlp=dense(32))],
+                   loop=(0, 1, 1)),
+    # sizes that are multiples of nothing in particular
+    "odd": config(52, 77, [ret(3, 10, 5, (0.9, 0.99, 0.97), rot_dims=6, mlp=moe(7, 7, 9)), lat(5, 6, 6, 7, 9, 13, 19, mlp=dense(30)),
+                           lat(3, 10, 2, 3, 11, 5, 4, mlp=moe(3, 2, 10))], loop=(1, 3, 2), eps=1e-5),
+}
+
+
+def write_folder(folder, cfg, seed, w=None):
+    from safetensors.torch import save_file
+    w = w if w is not None else pz.random_weights(cfg, seed)
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    save_file({k: v.contiguous() for k, v in w.items()}, os.path.join(folder, "model.safetensors"))
+    return w
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    out = {}
+    for i, (name, cfg) in enumerate(CONFIGS.items()):
+        d = str(tmp_path_factory.mktemp("zis_" + name))
+        out[name] = (d, cfg, write_folder(d, cfg, 31 + i))
+    return out
+
+
+_plain_cache = {}
+
+
+def plain_logits(name, cfg, w, seqs):
+    out = {}
+    for sid, toks in seqs.items():
+        key = (name, tuple(toks))
+        if key not in _plain_cache:
+            _plain_cache[key] = pz.forward(cfg, w, toks).float().numpy()
+        out[sid] = _plain_cache[key]
+    return out
+
+
+def row_errors(got, ref):
+    """Worst difference of a logits row (mean taken off, root mean square) in units of the
+    reference rows' root mean square; also where it is."""
+    rows = np.stack([ref[sid][p] for sid, p in got])
+    rms = float(np.sqrt((rows.astype(np.float64) ** 2).mean()))
+    worst, where = 0.0, None
+    for (sid, p), row in got.items():
+        d = row.astype(np.float64) - ref[sid][p]
+        d -= d.mean()
+        e = float(np.sqrt((d * d).mean())) / rms
+        if not e == e:
+            e = float("inf")
+        if e > worst:
+            worst, where = e, (sid, p)
+    return worst, where
+
+
+# bfloat16: what rounding alone does to these small models; the 32-bit runs carry the sharp bound
+BOUND = {"float32": 3e-5, "bfloat16": 8e-2}
+
+
+def make_runner(folder, dtype, steps, page_size=16, rows=4, **kw):
+    from sparseengine_b200.engine.factory import build_runner
+    tokens = tu.max_live_tokens(steps, round_to=page_size)
+    return build_runner(folder, dtype=dtype, page_size=page_size, num_pages=max(1, tokens // page_size), max_rows=rows,
+                        max_seq_len=max(64, tokens), **kw)
+
+
+def check_trace(folders, name, dtype, steps, seqs, what, bound=None, **kw):
+    folder, cfg, w = folders[name]
+    runner = make_runner(folder, dtype, steps, **kw)
+    got = tu.run_trace_runner(runner, steps)
+    from sparseengine_b200.csrc import ops
+    ops.error_check(runner.device)
+    runner.cache.check()
+    assert runner.cache.free_rows == runner.cache.max_rows
+    worst, where = row_errors(got, plain_logits(name, cfg, w, seqs))
+    assert worst < (bound or BOUND[dtype]), f"{what} ({name}, {dtype}): row error {worst:.3e} at {where}"
+    return runner
+
+
+def prompts(cfg, lengths, seed):
+    return {f"s{i}": tu.random_prompt(cfg["vocab"], n, seed + i) for i, n in enumerate(lengths)}
+
+
+# ---- each mechanism alone ----------------------------------------------------------------------
+
+SINGLE = {
+    "latent_attention": ([lat(4, 8, 8, 12, 10, 16, 9)], None),
+    "latent_attention_all_keys": ([lat(2, 8, 4, 8, 6, 12, None)], None),
+    "retention": ([ret(3, 12, 20, (0.8, 0.96, 0.999), rot_dims=6)], None),
+    "dense_feed_forward": ([ret(1, 4, 4, (0.5,), mlp=dense(80))], None),
+    "routed_feed_forward": ([ret(1, 4, 4, (0.5,), mlp=moe(6, 3, 16))], None),
+    "loop": ([ret(2, 8, 8, (0.9, 0.99)), lat(2, 8, 8, 8, 8, 8, 5)], (0, 2, 3)),
+}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("which", sorted(SINGLE))
+def test_each_mechanism_alone(tmp_path, which, dtype):
+    layers, loop = SINGLE[which]
+    cfg = config(40, 50, layers, loop=loop)
+    w = write_folder(str(tmp_path), cfg, 5)
+    seqs = prompts(cfg, (37, 1, 18), 3)
+    for cut in (tu.trace_whole, lambda s: tu.trace_chunks(s, sizes=(2, 3, 1, 5, 2)), lambda s: tu.trace_tail_decode(s, tail=9)):
+        check_trace({which: (str(tmp_path), cfg, w)}, which, dtype, cut(seqs), seqs, "alone")
+
+
+# ---- ways of cutting ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", sorted(CONFIGS))
+def test_whole_decode_chunks_mixed(folders, name, dtype):
+    cfg = CONFIGS[name]
+    seqs = prompts(cfg, (70, 33, 1, 18, 49, 2, 26), 20)
+    check_trace(folders, name, dtype, tu.trace_whole(seqs), seqs, "whole")
+    check_trace(folders, name, dtype, tu.trace_tail_decode(seqs, tail=20), seqs, "decode")
+    check_trace(folders, name, dtype, tu.trace_chunks(seqs), seqs, "portions")
+    check_trace(folders, name, dtype, tu.trace_chunks(seqs, sizes=(2,)), seqs, "portions of two")
+    # three rows for seven requests, and a pool of the live tokens only: rows, state slots and pages are used again
+    runner = check_trace(folders, name, dtype, tu.trace_mixed(seqs, live=3, chunk=6, decode_tail=5), seqs, "mixed", rows=3)
+    assert all(g.pool.reused_total > 0 for g in runner.cache.groups)
+    check_trace(folders, name, dtype, tu.trace_random(seqs, seed=3, live=4), seqs, "random schedule", page_size=8)
+
+
+def test_a_state_slot_that_is_used_again_starts_from_zero(folders):
+    """One row: every request gets the slot and the pages the one before it left; a long request
+    first, so that its state is far from zero."""
+    seqs = prompts(CONFIGS["middle"], (60, 5, 1, 9), 40)
+    check_trace(folders, "middle", "float32", tu.trace_chunks(seqs, sizes=(7, 2)), seqs, "one slot", rows=1)
+
+
+# ---- places where a fault would sit --------------------------------------------------------------
+
+def sharp_window_model(window, seed=9):
+    """One latent attention layer whose softmax is sharp (a large score scale), so that a query
+    hangs on the one or two keys of its window with the highest score: a key that is lost at the
+    window's far edge, or one that is let in from beyond it, moves the row by much."""
+    cfg = config(64, 80, [lat(4, 16, 16, 16, 24, 32, window, scale=2.5, mlp=dense(64))])
+    return cfg, pz.random_weights(cfg, seed)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_windows_two_edges_and_page_borders(tmp_path, dtype):
+    """Window 37 over pages of 16: the oldest key a query sees wanders through every place of a
+    page, in prompts, in portions that start and end anywhere, and in tokens decoded alone; pages
+    behind the window are given back and used again meanwhile.  (In bfloat16 the rounding of queries
+    and keys moves such sharp weights by itself, hence the wider bound; a lost key moves the row by
+    its whole size.)"""
+    cfg, w = sharp_window_model(37)
+    write_folder(str(tmp_path), cfg, 0, w)
+    seqs = prompts(cfg, (150, 37, 38, 36, 16, 95), 60)
+    fs = {"edge": (str(tmp_path), cfg, w)}
+    bound = 0.3 if dtype == "bfloat16" else None
+    check_trace(fs, "edge", dtype, tu.trace_whole(seqs), seqs, "window, whole", bound)
+    check_trace(fs, "edge", dtype, tu.trace_tail_decode(seqs, tail=60), seqs, "window, decoded", bound)
+    check_trace(fs, "edge", dtype, tu.trace_chunks(seqs, sizes=(15, 2, 16, 33, 1, 37, 38)), seqs, "window, portions", bound)
+    check_trace(fs, "edge", dtype, tu.trace_mixed(seqs, live=3, chunk=21, decode_tail=40), seqs, "window, mixed", bound, rows=3)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_heavy_sink(tmp_path, dtype):
+    """Sinks far above every score take almost all of the weight (outputs near zero), sinks far
+    below take none; both in one model, with windows of two keys and of one."""
+    cfg = config(48, 64, [lat(4, 8, 8, 8, 12, 16, 2), lat(4, 8, 8, 8, 12, 16, 1, mlp=dense(32))])
+    w = pz.random_weights(cfg, 4)
+    w["l0.mix.sink"] = torch.tensor([9.0, -30.0, 2.0, 0.0]).to(torch.bfloat16)
+    w["l1.mix.sink"] = torch.tensor([-2.0, 30.0, 0.5, -9.0]).to(torch.bfloat16)
+    write_folder(str(tmp_path), cfg, 0, w)
+    seqs = prompts(cfg, (21, 2, 1), 7)
+    fs = {"sink": (str(tmp_path), cfg, w)}
+    for cut in (tu.trace_whole, lambda s: tu.trace_chunks(s, sizes=(2, 1, 3)), lambda s: tu.trace_tail_decode(s, tail=12)):
+        check_trace(fs, "sink", dtype, cut(seqs), seqs, "sink")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_far_token_under_a_slow_decay(tmp_path, dtype):
+    """Retention heads with decays of 1 and just below keep the first tokens for good: the model's
+    only mixer is a retention, so a changed first token can reach position 400 through the state
+    alone.  A state that is lost at a portion's start or copied to the wrong slot shows there."""
+    cfg = config(48, 64, [ret(3, 16, 16, (1.0, 0.9995, 0.9), mlp=dense(64))])
+    w = pz.random_weights(cfg, 12)
+    write_folder(str(tmp_path), cfg, 0, w)
+    seqs = prompts(cfg, (420, 130, 3), 70)
+    changed = list(seqs["s0"])
+    changed[0] = (changed[0] + 1) % 64
+    a, b = pz.forward(cfg, w, seqs["s0"]), pz.forward(cfg, w, changed)
+    assert float((a[400:] - b[400:]).pow(2).mean().sqrt() / a.pow(2).mean().sqrt()) > 1e-3        # the premise
+    fs = {"far": (str(tmp_path), cfg, w)}
+    check_trace(fs, "far", dtype, tu.trace_whole(seqs), seqs, "far token, whole")
+    check_trace(fs, "far", dtype, tu.trace_chunks(seqs, sizes=(64, 2, 33, 7, 1)), seqs, "far token, portions")
+    check_trace(fs, "far", dtype, tu.trace_tail_decode(seqs, tail=40), seqs, "far token, decoded")
+    check_trace(fs, "far", dtype, tu.trace_mixed(seqs, live=2, chunk=50, decode_tail=10), seqs, "far token, mixed", rows=2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_first_tokens(folders, dtype):
+    """Requests of one to four tokens, whole, in portions of one and two, and side by side."""
+    seqs = prompts(CONFIGS["hybrid"], (1, 2, 3, 4, 1), 90)
+    check_trace(folders, "hybrid", dtype, tu.trace_whole(seqs), seqs, "first tokens")
+    check_trace(folders, "hybrid", dtype, tu.trace_chunks(seqs, sizes=(1, 2, 1)), seqs, "first tokens, portions")
+    check_trace(folders, "hybrid", dtype, tu.trace_mixed(seqs, live=4, chunk=2, decode_tail=1), seqs, "first tokens, mixed")
+
+
+def test_long_decoding_through_replayed_graphs(folders):
+    """140 tokens decoded one by one, far past every window, through replayed CUDA graphs."""
+    seqs = prompts(CONFIGS["hybrid"], (170, 150), 120)
+    steps = tu.trace_tail_decode(seqs, tail=140)
+    runner = check_trace(folders, "hybrid", "float32", steps, seqs, "long decoding")
+    assert runner.graph_replays > 200
+    check_trace(folders, "hybrid", "bfloat16", steps, seqs, "long decoding")
+
+
+def test_a_batch_does_not_change_a_request(folders):
+    """Unequal requests in one step against each alone: equal up to the order of sums in 32-bit."""
+    from sparseengine_b200.engine.runner import StepEntry
+    folder, cfg, w = folders["hybrid"]
+    seqs = prompts(cfg, (29, 3, 11), 140)
+    steps = [{"step": 0, "entries": [{"id": sid, "tokens": toks} for sid, toks in seqs.items()], "end": []}]
+    runner = make_runner(folder, "float32", steps, rows=4)       # pages for all three at once
+    alone = {}
+    for sid, toks in seqs.items():
+        runner.admit(sid)
+        runner.step([StepEntry(sid, toks[:-1], [])])
+        alone[sid] = runner.step([StepEntry(sid, toks[-1:], [0])]).clone()
+        runner.release(sid)
+    for sid in seqs:
+        runner.admit(sid)
+    runner.step([StepEntry(sid, toks[:-1], []) for sid, toks in seqs.items()])
+    together = runner.step([StepEntry(sid, toks[-1:], [0]) for sid, toks in seqs.items()])
+    for i, sid in enumerate(seqs):
+        assert float((together[i] - alone[sid][0]).abs().max()) < 2e-5 * float(alone[sid][0].abs().max()), sid
+
+
+def test_the_stream_after_every_layer_run(folders):
+    """The 32-bit stream after each visit of the execution order (a looped layer counts each time)
+    against the plain implementation's."""
+    from sparseengine_b200.engine.runner import StepEntry
+    folder, cfg, w = folders["middle"]
+    toks = tu.random_prompt(cfg["vocab"], 45, 8)
+    taps = []
+    pz.forward(cfg, w, toks, taps)
+    assert len(taps) == 1 + 3 * 2 + 1
+    runner = make_runner(folder, "float32", [{"step": 0, "entries": [{"id": "a", "tokens": toks}], "end": []}])
+    runner.model.stream_taps = got = []
+    runner.admit("a")
+    runner.step([StepEntry("a", toks, [0])])
+    assert len(got) == len(taps)
+    for i, (a, b) in enumerate(zip(got, taps)):
+        assert float((a.cpu().double() - b).abs().max()) < 3e-5 * float(b.abs().max()), i
+
+
+# ---- the entry point -----------------------------------------------------------------------------
+
+def plain_greedy(cfg, w, prompt, steps):
+    toks, out, margins = list(prompt), [], []
+    for _ in range(steps):
+        logits = pz.forward(cfg, w, toks)[-1]
+        top = torch.topk(logits, 2).values
+        margins.append(float(top[0] - top[1]))
+        out.append(int(logits.argmax()))
+        toks.append(out[-1])
+    return out, margins
+
+
+@pytest.mark.parametrize("name", ["hybrid", "odd"])
+def test_greedy_generation_through_the_entry_point(folders, name):
+    from sparseengine_b200 import LLM, SamplingParams
+    folder, cfg, w = folders[name]
+    llm = LLM(folder, dtype="float32", page_size=8, num_kvcache_slots=512, max_num_batched_tokens=16, max_model_len=128,
+              max_num_seqs_in_gpu=3)
+    ps = [tu.random_prompt(cfg["vocab"], n, 200 + n) for n in (5, 21, 9, 2, 14)]
+    outs = llm.generate(ps, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    for p, o in zip(ps, outs):
+        want, margins = plain_greedy(cfg, w, p, 10)
+        if min(margins) > 1e-4:
+            assert o["token_ids"] == want
+        else:       # a near-tie: the tokens up to it
+            k = next(i for i, m in enumerate(margins) if m <= 1e-4)
+            assert o["token_ids"][:k] == want[:k]
+    assert llm.is_finished() and llm.runner.cache.free_rows == llm.runner.cache.max_rows
+
+
+def test_trace_program(folders, tmp_path):
+    """bin/trace_run as a program on a folder of this design, pages and slots used again."""
+    folder, cfg, w = folders["wide"]
+    seqs = prompts(cfg, (40, 7, 22, 31, 3), 300)
+    steps = tu.trace_mixed(seqs, live=4, chunk=9, decode_tail=4)
+    for dtype in ("float32", "bfloat16"):
+        out = str(tmp_path / dtype)
+        got = tu.run_trace_cli(folder, dtype, steps, out, tu.max_live_tokens(steps))
+        worst, where = row_errors(got, plain_logits("wide", cfg, w, seqs))
+        assert worst < BOUND[dtype], (dtype, worst, where)
+
+
+def test_command_line(folders, tmp_path):
+    import subprocess
+    import sys
+    folder, cfg, w = folders["hybrid"]
+    hyper = json.dumps({"dtype": "bfloat16", "page_size": 8, "num_kvcache_slots": 1024, "max_model_len": 256})
+    for extra in ([], ["--tiny_random"]):
+        r = subprocess.run([sys.executable, "-m", "sparseengine_b200.cli.bench", "--model_path", folder, "--lengths", "24",
+                            "--batch_sizes", "3", "--output_len", "6", "--random_prompts", "--generate", "--hyper_params", hyper,
+                            *extra], cwd=tu.ROOT, capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, r.stderr[-2000:]
+        assert r.stdout.strip()
