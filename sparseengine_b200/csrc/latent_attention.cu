@@ -199,3 +199,299 @@ extern "C" int se_latent_attention_plain(const float* q_lat, const void* q, int 
 #undef SE_LAT_LAUNCH
     SE_LAUNCH_CHECK();
 }
+
+// ---- the tiled kernel (bfloat16) ------------------------------------------------------------------
+//
+// All heads share a position's cached row, so the rows of a score tile are (token, head) pairs,
+// token-major: a 64-row tile spans a few tokens and all their heads (or 64 heads of one token), and
+// every key tile brought to shared memory serves all of them: a decode step reads a request's
+// window once, not once per head.  Flash-attention loop on m16n8k16 tiles: the query tile stays in
+// shared memory (A fragments by ldmatrix), each of four warps owns 16 rows, key tiles of 64 rows
+// `[c | k_rot]` arrive by cp.async; S = Q K^T over all `D = rank + rot` dims, P V over the first
+// `rank` dims of the same tile (the latent is the value).  Scores, softmax and sums are 32-bit; the
+// sink joins a row's running maximum and sum before the first key.  Rows of the tile are stored
+// with a pitch of DMAX elements, chunks of 16 bytes XOR-swizzled.
+#include "mma_util.cuh"
+
+namespace se {
+namespace lat {
+
+constexpr int kTileKeys = 64;
+constexpr int kTileRows = 64;
+constexpr int kWarps = 4;
+constexpr int kThreads = 32 * kWarps;
+
+using namespace se::mma;
+
+// qfull[t, h, :] = [q_lat[h, t, :] | rotated part of q[t, h]] in bfloat16: the query rows as the tiled kernel reads them
+__global__ void latent_q_pack_kernel(const float* __restrict__ q_lat, const __nv_bfloat16* __restrict__ q, int d,
+                                     const float* __restrict__ inv_freq, int rotary_dim,
+                                     const int* __restrict__ positions, __nv_bfloat16* __restrict__ qfull, int tokens,
+                                     int heads, int rank, int rot) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const int D = rank + rot;
+    __nv_bfloat16* dst = qfull + ((size_t)t * heads + h) * D;
+    for (int i = threadIdx.x; i < rank; i += blockDim.x)
+        dst[i] = __float2bfloat16_rn(q_lat[((size_t)h * tokens + t) * rank + i]);
+    const __nv_bfloat16* qr = q + ((size_t)t * heads + h) * (d + rot) + d;
+    const int half = rotary_dim / 2;
+    const int pos = positions[t];
+    for (int i = threadIdx.x; i < rot; i += blockDim.x) {
+        float v = __bfloat162float(qr[i]);
+        if (i < rotary_dim) {
+            const int j = i < half ? i : i - half;
+            float sn, cs;
+            sincosf((float)pos * inv_freq[j], &sn, &cs);
+            const float u = __bfloat162float(qr[j]), w = __bfloat162float(qr[j + half]);
+            v = i < half ? u * cs - w * sn : w * cs + u * sn;
+        }
+        dst[rank + i] = __float2bfloat16_rn(v);
+    }
+}
+
+template <int DMAX, int STAGES>
+__global__ void __launch_bounds__(kThreads)
+latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __nv_bfloat16* __restrict__ cache,
+                              const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
+                              const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+                              const float* __restrict__ sink, __nv_bfloat16* __restrict__ out, int tokens, int heads,
+                              int rank, int rot, int page_size, float scale, int window, int num_pages,
+                              int* __restrict__ error) {
+    constexpr int kTileBytes = kTileKeys * DMAX * 2;
+    extern __shared__ __align__(128) uint8_t lat_tile_smem[];
+    uint8_t* q_smem = lat_tile_smem;                     // [kTileRows][DMAX]
+    uint8_t* k_smem = lat_tile_smem + kTileRows * DMAX * 2;   // [STAGES][kTileKeys][DMAX]
+    const int D = rank + rot;
+    const int chunks = D / 8;                            // 16-byte chunks of a row
+    const int d16 = D / 16, r16 = rank / 16;
+
+    const int entry = blockIdx.y;
+    const int tok0 = cu_q[entry];
+    const int q_len = cu_q[entry + 1] - tok0;
+    const int total_rows = q_len * heads;
+    const int row_base = (int)(gridDim.x - 1 - blockIdx.x) * kTileRows;     // the tiles with the most keys start first
+    if (row_base >= total_rows) return;
+    const int kv_end = kv_len[entry];
+    const int q_start = kv_end - q_len;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t4 = lane & 3;
+
+    int pos[2], tok[2], head[2], lo[2];
+    bool valid[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int row = row_base + warp * 16 + g + 8 * h;
+        valid[h] = row < total_rows;
+        const int r = valid[h] ? row : total_rows - 1;
+        tok[h] = tok0 + r / heads;
+        head[h] = r % heads;
+        pos[h] = q_start + r / heads;
+        lo[h] = window > 0 ? max(0, pos[h] - window + 1) : 0;
+    }
+    const int last_row = min(row_base + kTileRows, total_rows) - 1;
+    const int max_pos = q_start + last_row / heads;
+    const int first_pos = q_start + row_base / heads;
+    const int k_lo = window > 0 ? max(0, first_pos - window + 1) : 0;
+    const int k_begin = (k_lo / kTileKeys) * kTileKeys;
+    const int k_end = max_pos + 1;
+    const int num_tiles = (k_end - k_begin + kTileKeys - 1) / kTileKeys;
+    const int* row_table = table + (size_t)seq_rows[entry] * table_stride;
+
+    // the query tile: rows are contiguous in qfull ([tokens, heads, D], token-major)
+    {
+        const __nv_bfloat16* src = qfull + ((size_t)tok0 * heads + row_base) * D;
+        const int n_rows = min(kTileRows, total_rows - row_base);
+        for (int x = threadIdx.x; x < kTileRows * chunks; x += kThreads) {
+            const int r = x / chunks, c = x - r * chunks;
+            cp_async16(smem_u32(q_smem) + tile_off<DMAX>(r, c), src + (size_t)(r < n_rows ? r : 0) * D + c * 8, r < n_rows);
+        }
+    }
+    auto load_tile = [&](int tile, int stage) {
+        uint8_t* kbase = k_smem + (size_t)stage * kTileBytes;
+        const int base = k_begin + tile * kTileKeys;
+        for (int x = threadIdx.x; x < kTileKeys * chunks; x += kThreads) {
+            const int r = x / chunks, c = x - r * chunks;
+            const int j = base + r;
+            // clamped into what every row of the tile may see: rows outside are zero-filled, never read (a
+            // page behind the window may belong to another request by now)
+            const int jj = min(max(j, k_lo), k_end - 1);
+            const int page = row_table[jj / page_size];
+            const bool ok = page_in_pool(page, num_pages, error, 29) && j < k_end && j >= k_lo;
+            cp_async16(smem_u32(kbase) + tile_off<DMAX>(r, c),
+                       cache + ((size_t)(ok ? page : 0) * page_size + jj % page_size) * D + c * 8, ok);
+        }
+    };
+    for (int s = 0; s < STAGES - 1; ++s) {
+        if (s < num_tiles) load_tile(s, s);
+        cp_async_commit();                               // the first group also holds the query tile
+    }
+
+    float o[DMAX / 8][4];
+#pragma unroll
+    for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    // the sink: a logit of its own (not scaled) that joins the maximum and the sum; in units of the
+    // raw scores it is sink / scale
+    float m_run[2], l_run[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        m_run[h] = sink != nullptr ? sink[head[h]] / scale : -INFINITY;
+        l_run[h] = (sink != nullptr && t4 == 0) ? 1.f : 0.f;     // the four lanes of a row add their sums at the end
+    }
+    const float scale_log2 = scale * 1.4426950408889634f;
+    const int warp_last_row = min(row_base + warp * 16 + 15, total_rows - 1);
+    const int warp_max_pos = q_start + warp_last_row / heads;
+    const uint32_t qaddr = smem_u32(q_smem);
+
+    for (int tile = 0; tile < num_tiles; ++tile) {
+        cp_async_wait<STAGES - 2>();
+        __syncthreads();
+        if (tile + STAGES - 1 < num_tiles) load_tile(tile + STAGES - 1, (tile + STAGES - 1) % STAGES);
+        cp_async_commit();
+
+        const int key0 = k_begin + tile * kTileKeys;
+        if (key0 > warp_max_pos || row_base + warp * 16 >= total_rows) continue;       // warp-uniform
+        const uint32_t kaddr = smem_u32(k_smem + (size_t)(tile % STAGES) * kTileBytes);
+
+        float s[kTileKeys / 8][4];
+#pragma unroll
+        for (int n = 0; n < kTileKeys / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+        const int mat = lane >> 3, rr = lane & 7;
+#pragma unroll 4
+        for (int kk = 0; kk < d16; ++kk) {
+            uint32_t qa[4];
+            ldmatrix_x4(qaddr + tile_off<DMAX>(warp * 16 + (mat & 1) * 8 + rr, 2 * kk + (mat >> 1)), qa[0], qa[1], qa[2], qa[3]);
+#pragma unroll
+            for (int n2 = 0; n2 < kTileKeys / 16; ++n2) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(kaddr + tile_off<DMAX>(n2 * 16 + (mat >> 1) * 8 + rr, 2 * kk + (mat & 1)), b0, b1, b2, b3);
+                mma_bf16(s[2 * n2], qa, b0, b1);
+                mma_bf16(s[2 * n2 + 1], qa, b2, b3);
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int n = 0; n < kTileKeys / 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = key0 + n * 8 + 2 * t4 + (e & 1);
+                const int h = e >> 1;
+                if (j > pos[h] || j < lo[h]) s[n][e] = -INFINITY;
+                mx[h] = fmaxf(mx[h], s[n][e]);
+            }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m_run[h], mx[h]);
+            m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+            corr[h] = exp2f((m_run[h] - m_use[h]) * scale_log2);
+            m_run[h] = m_new;
+        }
+        float psum[2] = {0.f, 0.f};
+        uint32_t pa[kTileKeys / 16][4];
+#pragma unroll
+        for (int n = 0; n < kTileKeys / 8; ++n) {
+            const float p0 = exp2f((s[n][0] - m_use[0]) * scale_log2);
+            const float p1 = exp2f((s[n][1] - m_use[0]) * scale_log2);
+            const float p2 = exp2f((s[n][2] - m_use[1]) * scale_log2);
+            const float p3 = exp2f((s[n][3] - m_use[1]) * scale_log2);
+            psum[0] += p0 + p1;
+            psum[1] += p2 + p3;
+            pa[n >> 1][(n & 1) * 2 + 0] = pack_bf16(p0, p1);
+            pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * corr[h] + psum[h];
+#pragma unroll
+        for (int n2 = 0; n2 < DMAX / 16; ++n2) {
+            if (n2 < r16) {                              // the same for every thread
+                o[2 * n2][0] *= corr[0]; o[2 * n2][1] *= corr[0]; o[2 * n2][2] *= corr[1]; o[2 * n2][3] *= corr[1];
+                o[2 * n2 + 1][0] *= corr[0]; o[2 * n2 + 1][1] *= corr[0]; o[2 * n2 + 1][2] *= corr[1]; o[2 * n2 + 1][3] *= corr[1];
+#pragma unroll
+                for (int kk = 0; kk < kTileKeys / 16; ++kk) {
+                    uint32_t b0, b1, b2, b3;
+                    ldmatrix_x4_trans(kaddr + tile_off<DMAX>(kk * 16 + (mat & 1) * 8 + rr, 2 * n2 + (mat >> 1)), b0, b1, b2, b3);
+                    mma_bf16(o[2 * n2], pa[kk], b0, b1);
+                    mma_bf16(o[2 * n2 + 1], pa[kk], b2, b3);
+                }
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        if (!valid[h]) continue;
+        const float inv = 1.f / l_run[h];
+        __nv_bfloat16* dst = out + ((size_t)head[h] * tokens + tok[h]) * rank;
+#pragma unroll
+        for (int i = 0; i < DMAX / 8; ++i)
+            if (i < 2 * r16)
+                *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
+    }
+}
+
+template <int DMAX, int STAGES>
+static int launch_tiled(const void* qfull, const void* cache, const int* table, int table_stride, const int* seq_rows,
+                        const int* cu_q, const int* kv_len, const float* sink, void* out, int tokens, int entries,
+                        int max_q_len, int heads, int rank, int rot, int page_size, float scale, int window, int num_pages,
+                        int* error, cudaStream_t stream) {
+    const size_t smem = (size_t)(kTileRows + STAGES * kTileKeys) * DMAX * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(latent_attention_tiled_kernel<DMAX, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const long long row_tiles = ((long long)max_q_len * heads + kTileRows - 1) / kTileRows;
+    if (row_tiles > 0x7fffffffLL || entries > 65535) return SE_ERR_UNSUPPORTED;
+    dim3 grid((unsigned)row_tiles, entries);
+    latent_attention_tiled_kernel<DMAX, STAGES><<<grid, kThreads, smem, stream>>>(
+        (const __nv_bfloat16*)qfull, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len, sink,
+        (__nv_bfloat16*)out, tokens, heads, rank, rot, page_size, scale, window, num_pages, error);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace lat
+}  // namespace se
+
+// Sizes the tiled kernel takes: latent and rotated part in multiples of 16, a row of at most 256.
+extern "C" int se_latent_attention_tiled_supported(int rank, int rot) {
+    return rank > 0 && rot >= 0 && rank % 16 == 0 && rot % 16 == 0 && rank + rot <= 256;
+}
+
+extern "C" int se_latent_q_pack(const float* q_lat, const void* q, int d, const float* inv_freq, int rotary_dim,
+                                const int* positions, void* qfull, int tokens, int heads, int rank, int rot,
+                                cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (heads <= 0 || heads > 65535 || rotary_dim < 0 || rotary_dim > rot || (rotary_dim & 1)) return SE_ERR_ARGUMENT;
+    se::lat::latent_q_pack_kernel<<<dim3(tokens, heads), 64, 0, stream>>>(
+        q_lat, (const __nv_bfloat16*)q, d, inv_freq, rotary_dim, positions, (__nv_bfloat16*)qfull, tokens, heads, rank, rot);
+    SE_LAUNCH_CHECK();
+}
+
+// qfull: bfloat16 [tokens, heads, rank + rot]; out: bfloat16 [heads, tokens, rank]; cu_q: [entries + 1]
+// token offsets; kv_len: [entries] keys of each request once this step's rows are written.
+extern "C" int se_latent_attention_tiled(const void* qfull, const void* cache, const int* table, int table_stride,
+                                         const int* seq_rows, const int* cu_q, const int* kv_len, const float* sink,
+                                         void* out, int tokens, int entries, int max_q_len, int heads, int rank, int rot,
+                                         int page_size, float scale, int window, int num_pages, int* error,
+                                         cudaStream_t stream) {
+    if (entries <= 0 || max_q_len <= 0) return 0;
+    if (!se_latent_attention_tiled_supported(rank, rot) || heads <= 0) return SE_ERR_UNSUPPORTED;
+    if (!(scale > 0.f) || page_size <= 0) return SE_ERR_ARGUMENT;
+    if (rank + rot <= 128)
+        return se::lat::launch_tiled<128, 3>(qfull, cache, table, table_stride, seq_rows, cu_q, kv_len, sink, out, tokens,
+                                             entries, max_q_len, heads, rank, rot, page_size, scale, window, num_pages,
+                                             error, stream);
+    return se::lat::launch_tiled<256, 2>(qfull, cache, table, table_stride, seq_rows, cu_q, kv_len, sink, out, tokens,
+                                         entries, max_q_len, heads, rank, rot, page_size, scale, window, num_pages, error,
+                                         stream);
+}

@@ -316,6 +316,36 @@ def latent_attention_plain(q_lat, q, inv_freq, cache, table, seq_rows, token_seq
     return out
 
 
+def latent_attention_tiled_supported(rank: int, rot: int) -> bool:
+    """What ``se_latent_attention_tiled_supported`` answers, restated here so that asking does not compile
+    the kernel (a GPU test compares the two)."""
+    return rank > 0 and rot >= 0 and rank % 16 == 0 and rot % 16 == 0 and rank + rot <= 256
+
+
+def latent_q_pack(q_lat, q, inv_freq, positions, qfull, *, heads, head_dim, rank, rot, rotary_dim):
+    """``qfull[t, h] = [q_lat[h, t] | rotated part of q[t, h]]`` in bfloat16: the query rows of the tiled kernel."""
+    tokens = q.shape[0]
+    _check(_fn("se_latent_q_pack", "ppipi" "pp" "iiii" "p")(
+        _ptr(q_lat, torch.float32, "q_lat"), _ptr(q, torch.bfloat16, "q"), head_dim, _ptr(inv_freq, torch.float32, "inv_freq"),
+        rotary_dim, _ptr(positions, torch.int32, "positions"), _ptr(qfull, torch.bfloat16, "qfull"), tokens, heads, rank,
+        rot, _stream()), "latent_q_pack")
+    return qfull
+
+
+def latent_attention_tiled(qfull, cache, table, seq_rows, cu_q, kv_len, sink, out, *, entries, max_q_len, heads, rank, rot,
+                           page_size, scale, window=None, num_pages=None):
+    """bfloat16, tensor-core tiles; ``qfull`` [tokens, heads, rank + rot], ``out`` [heads, tokens, rank]."""
+    tokens = qfull.shape[0]
+    _check(_fn("se_latent_attention_tiled", "pppi" "ppp" "pp" "iiiiii" "i" "f" "ii" "p" "p")(
+        _ptr(qfull, torch.bfloat16, "qfull"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
+        table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(cu_q, torch.int32, "cu_q"),
+        _ptr(kv_len, torch.int32, "kv_len"), _ptr(sink, torch.float32, "sink"), _ptr(out, torch.bfloat16, "out"),
+        tokens, entries, max_q_len, heads, rank, rot, page_size, float(scale), int(window or 0),
+        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(qfull.device)), _stream()),
+        "latent_attention_tiled")
+    return out
+
+
 # ---- retention (csrc/retention.cu) ----------------------------------------------------------------
 
 def retention_prep(proj, q_off: int, k_off: int, inv_freq, positions, q32, k32, *, heads, head_dim, rotary_dim, k_scale):

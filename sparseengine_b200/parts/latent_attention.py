@@ -93,8 +93,23 @@ class LatentAttention(Mixer):
         heads_out = torch.bmm(out_lat, self.uv.view(H, s.v_head_dim, rank).transpose(1, 2))      # [H, tokens, dv]
         return linear(heads_out.transpose(0, 1).reshape(tokens, H * s.v_head_dim), self.o)
 
+    use_tensor_cores = None      # False: always the kernel with one block per (token, head)
+
     def attend(self, q_lat, q, inv_freq, rotary_dim, out_lat, step, slot):
+        """bfloat16 steps of sizes the tiled kernel takes (latent and rotated part in multiples of 16, a
+        cached row of at most 256) run on tensor-core tiles whose rows are (token, head) pairs, prompt
+        portions and single tokens alike; everything else one block per (token, head)."""
         s = self.spec
+        if (self.use_tensor_cores is not False and q.dtype == torch.bfloat16 and s.scale > 0
+                and ops.latent_attention_tiled_supported(s.kv_rank, s.rot_dim)):
+            qfull = torch.empty(q.shape[0], s.num_heads, s.kv_rank + s.rot_dim, dtype=q.dtype, device=q.device)
+            ops.latent_q_pack(q_lat, q, inv_freq, step.positions, qfull, heads=s.num_heads, head_dim=s.head_dim,
+                              rank=s.kv_rank, rot=s.rot_dim, rotary_dim=rotary_dim)
+            ops.latent_attention_tiled(qfull, slot.kv, slot.table, step.seq_rows, step.cu_q, step.kv_len, self.sink,
+                                       out_lat, entries=step.num_seqs, max_q_len=step.max_q_len, heads=s.num_heads,
+                                       rank=s.kv_rank, rot=s.rot_dim, page_size=slot.page_size, scale=s.scale,
+                                       window=s.window)
+            return
         ops.latent_attention_plain(q_lat, q, inv_freq, slot.kv, slot.table, step.seq_rows, step.token_seq,
                                    step.positions, self.sink, out_lat, heads=s.num_heads, head_dim=s.head_dim,
                                    rank=s.kv_rank, rot=s.rot_dim, rotary_dim=rotary_dim, page_size=slot.page_size,

@@ -377,3 +377,50 @@ def test_command_line(folders, tmp_path):
                             *extra], cwd=tu.ROOT, capture_output=True, text=True, timeout=300)
         assert r.returncode == 0, r.stderr[-2000:]
         assert r.stdout.strip()
+
+
+# ---- kernels against one another ---------------------------------------------------------------
+
+@pytest.mark.parametrize("rank,rot,heads,window", [(64, 32, 4, 33), (96, 32, 6, 70), (32, 16, 80, 5), (192, 64, 3, None), (16, 0, 1, 1)])
+def test_tiled_latent_attention_against_the_kernel_per_token_and_head(rank, rot, heads, window):
+    """The same queries, pages and block table through both kernels: portions that start anywhere
+    beside single tokens, pages in a shuffled order, windows that end inside a key tile; sinks that
+    take much, little and almost none of the weight."""
+    from sparseengine_b200.csrc import ops
+    dev, D, page = "cuda:0", rank + rot, 16
+    assert ops.latent_attention_tiled_supported(rank, rot) == bool(ops.library().se_latent_attention_tiled_supported(rank, rot))
+    g = torch.Generator(device=dev).manual_seed(rank + heads)
+    q_lens, kv_lens = [37, 1, 130, 1, 2], [37, 64, 209, 140, 17]
+    entries, tokens = len(q_lens), sum(q_lens)
+    max_pages = -(-max(kv_lens) // page)
+    perm = torch.randperm(entries * max_pages, generator=torch.Generator().manual_seed(1)).to(torch.int32)
+    table = perm.view(entries, max_pages).to(dev)
+    seq_rows = torch.tensor([3, 0, 4, 1, 2], dtype=torch.int32, device=dev)
+    table = table[torch.argsort(seq_rows.cpu()).to(dev)].contiguous()          # row seq_rows[e] holds entry e's pages
+    cache = (torch.randn(entries * max_pages, page, D, generator=g, device=dev) * 0.7).to(torch.bfloat16)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    positions = torch.cat([torch.arange(k - n, k) for n, k in zip(q_lens, kv_lens)]).to(torch.int32).to(dev)
+    token_seq = torch.repeat_interleave(torch.arange(entries), torch.tensor(q_lens)).to(torch.int32).to(dev)
+    cu_q = torch.tensor(cu, dtype=torch.int32, device=dev)
+    kv_len = torch.tensor(kv_lens, dtype=torch.int32, device=dev)
+    d = 8
+    q = torch.randn(tokens, heads * (d + rot), generator=g, device=dev).to(torch.bfloat16)
+    q_lat = torch.randn(heads, tokens, rank, generator=g, device=dev).to(torch.bfloat16).float()     # what the tiled kernel's rounding keeps
+    inv_freq = (10000.0 ** (-torch.arange(0, rot, 2, dtype=torch.float32) / max(rot, 1))).to(dev) if rot else None
+    sink = torch.linspace(-6.0, 4.0, heads, device=dev)
+    scale = D ** -0.5 * 2.0
+    plain = torch.empty(heads, tokens, rank, dtype=torch.bfloat16, device=dev)
+    ops.latent_attention_plain(q_lat, q, inv_freq, cache, table, seq_rows, token_seq, positions, sink, plain, heads=heads,
+                               head_dim=d, rank=rank, rot=rot, rotary_dim=rot, page_size=page, scale=scale, window=window)
+    qfull = torch.empty(tokens, heads, D, dtype=torch.bfloat16, device=dev)
+    ops.latent_q_pack(q_lat, q, inv_freq, positions, qfull, heads=heads, head_dim=d, rank=rank, rot=rot, rotary_dim=rot)
+    tiled = torch.full((heads, tokens, rank), float("nan"), dtype=torch.bfloat16, device=dev)
+    ops.latent_attention_tiled(qfull, cache, table, seq_rows, cu_q, kv_len, sink, tiled, entries=entries, max_q_len=max(q_lens),
+                               heads=heads, rank=rank, rot=rot, page_size=page, scale=scale, window=window)
+    ops.error_check(dev)
+    diff = (tiled.float() - plain.float()).abs()
+    assert bool(torch.isfinite(tiled.float()).all())
+    # the rotated part of the query and the weights are rounded to bfloat16 in the tiled kernel only
+    assert float(diff.max()) < 3e-2 * float(plain.float().abs().max()), float(diff.max())
