@@ -256,7 +256,8 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
                               const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                               const float* __restrict__ sink, __nv_bfloat16* __restrict__ out, int tokens, int heads,
                               int rank, int rot, int page_size, float scale, int window, int num_pages,
-                              int* __restrict__ error) {
+                              int* __restrict__ error, int splits, int tiles_per_split, float* __restrict__ part_o,
+                              float* __restrict__ part_ml) {
     constexpr int kTileBytes = kTileKeys * DMAX * 2;
     extern __shared__ __align__(128) uint8_t lat_tile_smem[];
     uint8_t* q_smem = lat_tile_smem;                     // [kTileRows][DMAX]
@@ -296,6 +297,11 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
     const int k_end = max_pos + 1;
     const int num_tiles = (k_end - k_begin + kTileKeys - 1) / kTileKeys;
     const int* row_table = table + (size_t)seq_rows[entry] * table_stride;
+    // with several splits, CTA z takes the key tiles [t_begin, t_end) and leaves unnormalised sums
+    // with their maximum for the merge kernel, which also brings the sink in
+    const int t_begin = splits > 1 ? min(num_tiles, (int)blockIdx.z * tiles_per_split) : 0;
+    const int t_end = splits > 1 ? min(num_tiles, t_begin + tiles_per_split) : num_tiles;
+    const bool with_sink = sink != nullptr && splits == 1;
 
     // the query tile: rows are contiguous in qfull ([tokens, heads, D], token-major)
     {
@@ -322,7 +328,7 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
         }
     };
     for (int s = 0; s < STAGES - 1; ++s) {
-        if (s < num_tiles) load_tile(s, s);
+        if (t_begin + s < t_end) load_tile(t_begin + s, s);
         cp_async_commit();                               // the first group also holds the query tile
     }
 
@@ -334,23 +340,23 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
     float m_run[2], l_run[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        m_run[h] = sink != nullptr ? sink[head[h]] / scale : -INFINITY;
-        l_run[h] = (sink != nullptr && t4 == 0) ? 1.f : 0.f;     // the four lanes of a row add their sums at the end
+        m_run[h] = with_sink ? sink[head[h]] / scale : -INFINITY;
+        l_run[h] = (with_sink && t4 == 0) ? 1.f : 0.f;           // the four lanes of a row add their sums at the end
     }
     const float scale_log2 = scale * 1.4426950408889634f;
     const int warp_last_row = min(row_base + warp * 16 + 15, total_rows - 1);
     const int warp_max_pos = q_start + warp_last_row / heads;
     const uint32_t qaddr = smem_u32(q_smem);
 
-    for (int tile = 0; tile < num_tiles; ++tile) {
+    for (int tile = t_begin; tile < t_end; ++tile) {
         cp_async_wait<STAGES - 2>();
         __syncthreads();
-        if (tile + STAGES - 1 < num_tiles) load_tile(tile + STAGES - 1, (tile + STAGES - 1) % STAGES);
+        if (tile + STAGES - 1 < t_end) load_tile(tile + STAGES - 1, (tile - t_begin + STAGES - 1) % STAGES);
         cp_async_commit();
 
         const int key0 = k_begin + tile * kTileKeys;
         if (key0 > warp_max_pos || row_base + warp * 16 >= total_rows) continue;       // warp-uniform
-        const uint32_t kaddr = smem_u32(k_smem + (size_t)(tile % STAGES) * kTileBytes);
+        const uint32_t kaddr = smem_u32(k_smem + (size_t)((tile - t_begin) % STAGES) * kTileBytes);
 
         float s[kTileKeys / 8][4];
 #pragma unroll
@@ -425,6 +431,19 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
     }
+    if (splits > 1) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            if (!valid[h]) continue;
+            const size_t at = ((size_t)tok[h] * heads + head[h]) * splits + blockIdx.z;
+            if (t4 == 0) { part_ml[2 * at] = m_run[h]; part_ml[2 * at + 1] = l_run[h]; }
+            float* dst = part_o + at * rank;
+#pragma unroll
+            for (int i = 0; i < DMAX / 8; ++i)
+                if (i < 2 * r16) *reinterpret_cast<float2*>(dst + i * 8 + 2 * t4) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
+        }
+        return;
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         if (!valid[h]) continue;
@@ -437,11 +456,35 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
     }
 }
 
+// One block per (token, head): the splits' sums brought to one maximum, the sink added once.
+__global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                              const float* __restrict__ sink, __nv_bfloat16* __restrict__ out, int tokens,
+                                              int heads, int rank, int splits, float scale) {
+    const int t = blockIdx.x, h = blockIdx.y;
+    const size_t at = ((size_t)t * heads + h) * splits;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    float mt = sink != nullptr ? sink[h] / scale : -INFINITY;
+    for (int z = 0; z < splits; ++z) mt = fmaxf(mt, part_ml[2 * (at + z)]);
+    float lt = sink != nullptr ? exp2f((sink[h] / scale - mt) * scale_log2) : 0.f;
+    for (int z = 0; z < splits; ++z) {
+        const float m = part_ml[2 * (at + z)];
+        if (m != -INFINITY) lt += part_ml[2 * (at + z) + 1] * exp2f((m - mt) * scale_log2);
+    }
+    for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+        float o = 0.f;
+        for (int z = 0; z < splits; ++z) {
+            const float m = part_ml[2 * (at + z)];
+            if (m != -INFINITY) o += part_o[(at + z) * rank + c] * exp2f((m - mt) * scale_log2);
+        }
+        out[((size_t)h * tokens + t) * rank + c] = __float2bfloat16_rn(o / lt);
+    }
+}
+
 template <int DMAX, int STAGES>
 static int launch_tiled(const void* qfull, const void* cache, const int* table, int table_stride, const int* seq_rows,
                         const int* cu_q, const int* kv_len, const float* sink, void* out, int tokens, int entries,
                         int max_q_len, int heads, int rank, int rot, int page_size, float scale, int window, int num_pages,
-                        int* error, cudaStream_t stream) {
+                        int* error, int splits, int tiles_per_split, float* part_o, float* part_ml, cudaStream_t stream) {
     const size_t smem = (size_t)(kTileRows + STAGES * kTileKeys) * DMAX * 2;
     static bool configured = false;
     if (!configured) {
@@ -452,10 +495,14 @@ static int launch_tiled(const void* qfull, const void* cache, const int* table, 
     }
     const long long row_tiles = ((long long)max_q_len * heads + kTileRows - 1) / kTileRows;
     if (row_tiles > 0x7fffffffLL || entries > 65535) return SE_ERR_UNSUPPORTED;
-    dim3 grid((unsigned)row_tiles, entries);
+    dim3 grid((unsigned)row_tiles, entries, splits);
     latent_attention_tiled_kernel<DMAX, STAGES><<<grid, kThreads, smem, stream>>>(
         (const __nv_bfloat16*)qfull, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len, sink,
-        (__nv_bfloat16*)out, tokens, heads, rank, rot, page_size, scale, window, num_pages, error);
+        (__nv_bfloat16*)out, tokens, heads, rank, rot, page_size, scale, window, num_pages, error, splits, tiles_per_split,
+        part_o, part_ml);
+    if (splits > 1)
+        latent_attention_merge_kernel<<<dim3(tokens, heads), 64, 0, stream>>>(part_o, part_ml, sink, (__nv_bfloat16*)out,
+                                                                             tokens, heads, rank, splits, scale);
     return (int)cudaGetLastError();
 }
 
@@ -479,19 +526,23 @@ extern "C" int se_latent_q_pack(const float* q_lat, const void* q, int d, const 
 
 // qfull: bfloat16 [tokens, heads, rank + rot]; out: bfloat16 [heads, tokens, rank]; cu_q: [entries + 1]
 // token offsets; kv_len: [entries] keys of each request once this step's rows are written.
+// splits > 1: the key tiles a row tile sees are dealt to `splits` CTAs, `tiles_per_split` tiles of 64 keys
+// each (steps of few rows over long windows); part_o: float [tokens * heads * splits * rank], part_ml:
+// float [tokens * heads * splits * 2].
 extern "C" int se_latent_attention_tiled(const void* qfull, const void* cache, const int* table, int table_stride,
                                          const int* seq_rows, const int* cu_q, const int* kv_len, const float* sink,
                                          void* out, int tokens, int entries, int max_q_len, int heads, int rank, int rot,
-                                         int page_size, float scale, int window, int num_pages, int* error,
-                                         cudaStream_t stream) {
+                                         int page_size, float scale, int window, int num_pages, int* error, int splits,
+                                         int tiles_per_split, float* part_o, float* part_ml, cudaStream_t stream) {
     if (entries <= 0 || max_q_len <= 0) return 0;
-    if (!se_latent_attention_tiled_supported(rank, rot) || heads <= 0) return SE_ERR_UNSUPPORTED;
-    if (!(scale > 0.f) || page_size <= 0) return SE_ERR_ARGUMENT;
+    if (!se_latent_attention_tiled_supported(rank, rot) || heads <= 0 || heads > 65535) return SE_ERR_UNSUPPORTED;
+    if (!(scale > 0.f) || page_size <= 0 || splits < 1 || splits > 65535) return SE_ERR_ARGUMENT;
+    if (splits > 1 && (tiles_per_split < 1 || part_o == nullptr || part_ml == nullptr)) return SE_ERR_ARGUMENT;
     if (rank + rot <= 128)
         return se::lat::launch_tiled<128, 3>(qfull, cache, table, table_stride, seq_rows, cu_q, kv_len, sink, out, tokens,
                                              entries, max_q_len, heads, rank, rot, page_size, scale, window, num_pages,
-                                             error, stream);
+                                             error, splits, tiles_per_split, part_o, part_ml, stream);
     return se::lat::launch_tiled<256, 2>(qfull, cache, table, table_stride, seq_rows, cu_q, kv_len, sink, out, tokens,
                                          entries, max_q_len, heads, rank, rot, page_size, scale, window, num_pages, error,
-                                         stream);
+                                         splits, tiles_per_split, part_o, part_ml, stream);
 }

@@ -332,17 +332,46 @@ def latent_q_pack(q_lat, q, inv_freq, positions, qfull, *, heads, head_dim, rank
     return qfull
 
 
+def latent_split_plan(row_tiles: int, entries: int, max_keys: int, sms: Optional[int] = None):
+    """How many CTAs share a row tile's keys, and how many 64-key tiles each takes.  Steps whose row
+    tiles alone do not fill the device twice over (decode, short portions) over windows of several
+    tiles are split along the keys; the merge kernel joins the parts."""
+    if sms is None:
+        sms = sm_count()
+    tiles = -(-max_keys // 64) + 1                      # a window may straddle one more tile
+    ctas = max(1, row_tiles * entries)
+    if ctas >= 2 * sms or tiles < 4:
+        return 1, tiles
+    splits = min(-(-2 * sms // ctas), tiles // 2)
+    per = -(-tiles // splits)
+    return -(-tiles // per), per
+
+
 def latent_attention_tiled(qfull, cache, table, seq_rows, cu_q, kv_len, sink, out, *, entries, max_q_len, heads, rank, rot,
-                           page_size, scale, window=None, num_pages=None):
-    """bfloat16, tensor-core tiles; ``qfull`` [tokens, heads, rank + rot], ``out`` [heads, tokens, rank]."""
+                           page_size, scale, window=None, num_pages=None, max_keys=None, splits=None):
+    """bfloat16, tensor-core tiles; ``qfull`` [tokens, heads, rank + rot], ``out`` [heads, tokens, rank].
+    ``max_keys``: an upper bound of the keys a query of this step sees (window, or the longest
+    request); with it, steps of few rows are split along the keys (``splits`` forces a count)."""
     tokens = qfull.shape[0]
-    _check(_fn("se_latent_attention_tiled", "pppi" "ppp" "pp" "iiiiii" "i" "f" "ii" "p" "p")(
+    row_tiles = -(-max_q_len * heads // 64)
+    per = 0
+    if splits is None:
+        splits, per = latent_split_plan(row_tiles, entries, max_keys, sm_count(qfull.device)) if max_keys else (1, 0)
+    elif splits > 1:
+        per = -(-(-(-(max_keys or 0) // 64) + 1) // splits)
+    part_o = part_ml = None
+    if splits > 1:
+        part_o = torch.empty(tokens * heads * splits * rank, dtype=torch.float32, device=qfull.device)
+        part_ml = torch.empty(tokens * heads * splits * 2, dtype=torch.float32, device=qfull.device)
+    global launch_count
+    launch_count += 1 if splits > 1 else 0
+    _check(_fn("se_latent_attention_tiled", "pppi" "ppp" "pp" "iiiiii" "i" "f" "ii" "p" "iipp" "p")(
         _ptr(qfull, torch.bfloat16, "qfull"), _ptr(cache, torch.bfloat16, "cache"), _ptr(table, torch.int32, "table"),
         table.shape[1], _ptr(seq_rows, torch.int32, "seq_rows"), _ptr(cu_q, torch.int32, "cu_q"),
         _ptr(kv_len, torch.int32, "kv_len"), _ptr(sink, torch.float32, "sink"), _ptr(out, torch.bfloat16, "out"),
         tokens, entries, max_q_len, heads, rank, rot, page_size, float(scale), int(window or 0),
-        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(qfull.device)), _stream()),
-        "latent_attention_tiled")
+        cache.shape[0] if num_pages is None else int(num_pages), _ptr(error_word(qfull.device)), int(splits), int(per),
+        _ptr(part_o), _ptr(part_ml), _stream()), "latent_attention_tiled")
     return out
 
 
@@ -362,6 +391,17 @@ def retention_scan(q32, k32, proj, v_off: int, decay, state, step, o, *, heads, 
         _ptr(decay, torch.float32, "decay"), _ptr(state, torch.float32, "state"), state.stride(0), _ptr(step.cu_q),
         _ptr(step.seq_rows), _ptr(o, torch.float32, "o"), step.num_seqs, heads, head_dim, v_head_dim,
         dtype_code(proj.dtype), _stream()), "retention_scan")
+    return o
+
+
+def retention_chunk(q32, k32, proj, v_off: int, decay, state, step, o, *, heads, head_dim, v_head_dim):
+    """The same recurrence as :func:`retention_scan` in chunks of 64 tokens (closed form per chunk, 32-bit
+    FMA arithmetic): for steps that bring prompt portions."""
+    _check(_fn("se_retention_chunk", "pp" "pii" "p" "pl" "pp" "p" "iiii" "ip")(
+        _ptr(q32, torch.float32, "q32"), _ptr(k32, torch.float32, "k32"), proj.data_ptr(), proj.stride(0), int(v_off),
+        _ptr(decay, torch.float32, "decay"), _ptr(state, torch.float32, "state"), state.stride(0), _ptr(step.cu_q),
+        _ptr(step.seq_rows), _ptr(o, torch.float32, "o"), step.num_seqs, heads, head_dim, v_head_dim,
+        dtype_code(proj.dtype), _stream()), "retention_chunk")
     return o
 
 

@@ -120,6 +120,133 @@ retention_scan_kernel(const float* __restrict__ q32, const float* __restrict__ k
     }
 }
 
+// ---- prompt portions: the recurrence in chunks of 64 tokens ---------------------------------------
+//
+// With a fixed decay g the recurrence over a chunk of n tokens (local index t, s) has a closed form:
+//
+//     o_t   = g^(t+1) S_0^T q_t + sum_{s <= t} g^(t-s) (q_t . k_s) v_s
+//     S_new = g^n S_0 + sum_s g^(n-1-s) k_s v_s^T
+//
+// which is three small matrix products per chunk instead of a chain of n dependent steps.  All of it
+// is 32-bit FMA arithmetic (scores, decays and state enter the recurrence in 32-bit).  One block per
+// (entry, head, 32 value columns): q and k of the chunk lie transposed in shared memory (`[dim][token]`,
+// groups of four tokens XOR-swizzled by the dim so that both the transposing store and the 16-byte
+// reads spread over the banks), the block's slice of the state stays in shared memory over all chunks.
+constexpr int kChunk = 64;
+constexpr int kChunkThreads = 256;
+
+__device__ __forceinline__ int swz(int i, int t) { return i * kChunk + ((((t >> 2) ^ (i & 15)) << 2) | (t & 3)); }
+
+template <typename T>
+__global__ void __launch_bounds__(kChunkThreads)
+retention_chunk_kernel(const float* __restrict__ q32, const float* __restrict__ k32, const T* proj, int proj_stride,
+                       int v_off, const float* __restrict__ decay, float* state, long long state_stride,
+                       const int* __restrict__ cu_q, const int* __restrict__ seq_rows, float* __restrict__ o, int heads,
+                       int d, int dv) {
+    extern __shared__ __align__(16) float chunk_smem[];
+    float* qs = chunk_smem;                      // [d][64] swizzled
+    float* ks = qs + d * kChunk;                 // [d][64] swizzled
+    float* vs = ks + d * kChunk;                 // [64][32]
+    float* As = vs + kChunk * 32;                // [64 s][64 t]: g^(t-s) q_t . k_s for s <= t, else 0
+    float* Ss = As + kChunk * kChunk;            // [d][32]
+    float* gp = Ss + d * 32;                     // [65] powers of the decay
+    const int e = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
+    const int lane = threadIdx.x & 31, wg = threadIdx.x >> 5;
+    const int t_first = cu_q[e], t_last = cu_q[e + 1];
+    if (t_last <= t_first) return;
+    const double g = (double)decay[h];
+    for (int j = threadIdx.x; j <= kChunk; j += kChunkThreads) gp[j] = (float)pow(g, (double)j);
+    float* S = state + (size_t)seq_rows[e] * state_stride + (size_t)h * d * dv;
+    const bool col_ok = c0 + lane < dv;
+    for (int x = threadIdx.x; x < d * 32; x += kChunkThreads) Ss[x] = (c0 + (x & 31) < dv) ? S[(size_t)(x >> 5) * dv + c0 + (x & 31)] : 0.f;
+
+    for (int tb = t_first; tb < t_last; tb += kChunk) {
+        const int n = min(kChunk, t_last - tb);
+        __syncthreads();                          // the chunk before is done with q, k, v and A; the state is up to date
+        for (int x = threadIdx.x; x < kChunk * d; x += kChunkThreads) {
+            const int t = x / d, i = x - t * d;
+            const size_t at = ((size_t)(tb + t) * heads + h) * d + i;
+            qs[swz(i, t)] = t < n ? q32[at] : 0.f;
+            ks[swz(i, t)] = t < n ? k32[at] : 0.f;
+        }
+        for (int x = threadIdx.x; x < kChunk * 32; x += kChunkThreads) {
+            const int t = x >> 5, c = x & 31;
+            vs[x] = (t < n && c0 + c < dv) ? to_float(proj[(size_t)(tb + t) * proj_stride + v_off + h * dv + c0 + c]) : 0.f;
+        }
+        __syncthreads();
+        // scores of the chunk with their decays: a 4 x 4 tile per thread, tiles above the diagonal are zero
+        {
+            const int tt = (threadIdx.x >> 4) * 4, ss = (threadIdx.x & 15) * 4;
+            float acc[4][4] = {};
+            if (ss <= tt + 3) {
+                for (int i = 0; i < d; ++i) {
+                    const float4 qv = *reinterpret_cast<const float4*>(qs + swz(i, tt));
+                    const float4 kv = *reinterpret_cast<const float4*>(ks + swz(i, ss));
+                    const float qa[4] = {qv.x, qv.y, qv.z, qv.w}, ka[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+                    for (int a = 0; a < 4; ++a)
+#pragma unroll
+                        for (int b = 0; b < 4; ++b) acc[a][b] += qa[a] * ka[b];
+                }
+            }
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+                float4 row;
+                float* r = &row.x;
+#pragma unroll
+                for (int a = 0; a < 4; ++a) r[a] = (ss + b <= tt + a) ? acc[a][b] * gp[tt + a - ss - b] : 0.f;
+                *reinterpret_cast<float4*>(As + (ss + b) * kChunk + tt) = row;
+            }
+        }
+        float vreg[kChunk];                        // this lane's value column of the chunk
+#pragma unroll
+        for (int s_ = 0; s_ < kChunk; ++s_) vreg[s_] = vs[s_ * 32 + lane];
+        __syncthreads();
+        // outputs: warp wg takes tokens 8 wg .. 8 wg + 7, lane c the column
+        {
+            const int tg = wg * 8;
+            float acc[8] = {}, acc2[8] = {};
+#pragma unroll
+            for (int s_ = 0; s_ < kChunk; ++s_) {
+                const float4 a0 = *reinterpret_cast<const float4*>(As + s_ * kChunk + tg);
+                const float4 a1 = *reinterpret_cast<const float4*>(As + s_ * kChunk + tg + 4);
+                const float v = vreg[s_];
+                acc[0] += a0.x * v; acc[1] += a0.y * v; acc[2] += a0.z * v; acc[3] += a0.w * v;
+                acc[4] += a1.x * v; acc[5] += a1.y * v; acc[6] += a1.z * v; acc[7] += a1.w * v;
+            }
+            for (int i = 0; i < d; ++i) {
+                const float4 q0 = *reinterpret_cast<const float4*>(qs + swz(i, tg));
+                const float4 q1 = *reinterpret_cast<const float4*>(qs + swz(i, tg + 4));
+                const float sv = Ss[i * 32 + lane];
+                acc2[0] += q0.x * sv; acc2[1] += q0.y * sv; acc2[2] += q0.z * sv; acc2[3] += q0.w * sv;
+                acc2[4] += q1.x * sv; acc2[5] += q1.y * sv; acc2[6] += q1.z * sv; acc2[7] += q1.w * sv;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int t = tg + j;
+                if (t < n && col_ok) o[((size_t)(tb + t) * heads + h) * dv + c0 + lane] = acc[j] + gp[t + 1] * acc2[j];
+            }
+        }
+        __syncthreads();                          // every read of the old state is done
+        // the state after the chunk: warp wg takes rows wg, wg + 8, ...
+#pragma unroll
+        for (int s_ = 0; s_ < kChunk; ++s_) vreg[s_] = s_ < n ? vreg[s_] * gp[n - 1 - s_] : 0.f;
+        const float gn = gp[n];
+        for (int i = wg; i < d; i += kChunkThreads / 32) {
+            float a = 0.f;
+#pragma unroll
+            for (int s4 = 0; s4 < kChunk; s4 += 4) {
+                const float4 kv = *reinterpret_cast<const float4*>(ks + swz(i, s4));
+                a += kv.x * vreg[s4] + kv.y * vreg[s4 + 1] + kv.z * vreg[s4 + 2] + kv.w * vreg[s4 + 3];
+            }
+            Ss[i * 32 + lane] = gn * Ss[i * 32 + lane] + a;
+        }
+    }
+    __syncthreads();
+    for (int x = threadIdx.x; x < d * 32; x += kChunkThreads)
+        if (c0 + (x & 31) < dv) S[(size_t)(x >> 5) * dv + c0 + (x & 31)] = Ss[x];
+}
+
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]); a warp per (token, head).
 template <typename T>
 __global__ void retention_out_kernel(const float* __restrict__ o, const T* proj, int proj_stride, int g_off,
@@ -174,6 +301,27 @@ extern "C" int se_retention_scan(const float* q32, const float* k32, const void*
         else SE_RET_LAUNCH(32);
     });
 #undef SE_RET_LAUNCH
+    SE_LAUNCH_CHECK();
+}
+
+// The same recurrence in chunks of 64 tokens (closed form per chunk): for steps with prompt portions.
+extern "C" int se_retention_chunk_supported(int d) { return d > 0 && d <= 256; }
+
+extern "C" int se_retention_chunk(const float* q32, const float* k32, const void* proj, int proj_stride, int v_off,
+                                  const float* decay, float* state, long long state_stride, const int* cu_q,
+                                  const int* seq_rows, float* o, int entries, int heads, int d, int dv, int dtype,
+                                  cudaStream_t stream) {
+    if (entries <= 0) return 0;
+    if (!se_retention_chunk_supported(d) || dv <= 0 || heads <= 0 || heads > 65535 || (dv + 31) / 32 > 65535)
+        return SE_ERR_UNSUPPORTED;
+    dim3 grid(entries, heads, (dv + 31) / 32);
+    const size_t smem = (size_t)(2 * d * se::kChunk + se::kChunk * 32 + se::kChunk * se::kChunk + d * 32 + se::kChunk + 4) * sizeof(float);
+    SE_DISPATCH_DTYPE(dtype, T, {
+        cudaError_t e = cudaFuncSetAttribute(se::retention_chunk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        se::retention_chunk_kernel<T><<<grid, se::kChunkThreads, smem, stream>>>(
+            q32, k32, (const T*)proj, proj_stride, v_off, decay, state, state_stride, cu_q, seq_rows, o, heads, d, dv);
+    });
     SE_LAUNCH_CHECK();
 }
 

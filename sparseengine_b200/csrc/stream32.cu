@@ -96,21 +96,54 @@ __global__ void add_rmsnorm_stream_kernel(const float* x, const T* y, const T* _
     extern __shared__ __align__(16) float row[];
     __shared__ float scratch[33];
     const size_t base = (size_t)blockIdx.x * hidden;
+    // rows whose width is a multiple of 8 and whose pointers allow it move in groups of 8 elements
+    const bool vec = (hidden & 7) == 0 && aligned8(x) && (y == nullptr || aligned8(y)) && (w == nullptr || aligned8(w)) &&
+                     (out32 == nullptr || aligned8(out32)) && (out_act == nullptr || aligned8(out_act));
     float ss = 0.f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float v = x[base + i];
-        if (y != nullptr) v += to_float(y[base + i]);
-        row[i] = v;
-        ss += v * v;
-        if (out32 != nullptr) out32[base + i] = v;
+    if (vec) {
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float v[8];
+            load8(x + base + i, v);
+            if (y != nullptr) {
+                float r[8];
+                load8(y + base + i, r);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[j] += r[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { row[i + j] = v[j]; ss += v[j] * v[j]; }
+            if (out32 != nullptr) store8(out32 + base + i, v);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            float v = x[base + i];
+            if (y != nullptr) v += to_float(y[base + i]);
+            row[i] = v;
+            ss += v * v;
+            if (out32 != nullptr) out32[base + i] = v;
+        }
     }
     if (out_act == nullptr) return;
-    if (w == nullptr) {
-        for (int i = threadIdx.x; i < hidden; i += blockDim.x) out_act[base + i] = from_float<T>(row[i]);   // its own writes
-        return;
+    // every thread reads back the elements of the row that it wrote itself
+    const float inv = w != nullptr ? 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps) : 1.f;
+    if (vec) {
+        for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+            float o[8];
+            if (w != nullptr) {
+                float wv[8];
+                load8(w + i, wv);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = row[i + j] * inv * wv[j];
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = row[i + j];
+            }
+            store8(out_act + base + i, o);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+            out_act[base + i] = from_float<T>(w != nullptr ? row[i] * inv * to_float(w[i]) : row[i]);
     }
-    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)hidden + eps);
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out_act[base + i] = from_float<T>(row[i] * inv * to_float(w[i]));
 }
 
 __device__ __forceinline__ float act_apply(float v, int kind) {

@@ -81,7 +81,8 @@ KERNEL_TUNING_KEYS = {
     "gemv_max_rows": None,                                              # ... and so do projections of more rows than this
     "router_tensor_core_min_tokens": "split_router_min_tokens",         # prompt steps from this size take router logits from tensor cores
     "moe_pair_min_rows": "pair_min_rows",                               # (token, slot) rows from which experts may run on pairs of SMs
-    "moe_pair_min_rows_per_expert": "pair_min_rows_per_expert",         # ... if the experts that get rows have this many each
+    "moe_pair_min_rows_per_expert": "pair_min_rows_per_expert",
+    "retention_chunk_min_tokens": "chunk_min_tokens",                   # steps whose longest entry has this many tokens take the chunked recurrence         # ... if the experts that get rows have this many each
 }
 
 

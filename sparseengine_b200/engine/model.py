@@ -172,6 +172,13 @@ class Model:
                 y = timed("feed_forward", block.feed_forward.forward, hidden, step) if block.feed_forward is not None else None
                 hidden, residual = timed("feed_forward_norm", block.feed_forward_norm.forward_stream, residual, y, block.alpha)
             return hidden, residual
+        if isinstance(block, PreNormStreamBlock):
+            x, residual = timed("mixer_norm", block.mixer_norm.forward_stream, residual, hidden)
+            hidden = timed("mixer." + block.mixer.spec.kind, block.mixer.forward, x, step, slot)
+            if block.feed_forward is not None:
+                x, residual = timed("feed_forward_norm", block.feed_forward_norm.forward_stream, residual, hidden)
+                hidden = timed("feed_forward." + block.feed_forward.spec.kind, block.feed_forward.forward, x, step)
+            return hidden, residual
         if not isinstance(block, PreNormBlock):
             return timed("block", block.forward, hidden, residual, step, slot)
         x, residual = timed("mixer_norm", block.mixer_norm.forward, hidden, residual)

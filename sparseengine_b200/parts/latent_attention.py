@@ -108,7 +108,8 @@ class LatentAttention(Mixer):
             ops.latent_attention_tiled(qfull, slot.kv, slot.table, step.seq_rows, step.cu_q, step.kv_len, self.sink,
                                        out_lat, entries=step.num_seqs, max_q_len=step.max_q_len, heads=s.num_heads,
                                        rank=s.kv_rank, rot=s.rot_dim, page_size=slot.page_size, scale=s.scale,
-                                       window=s.window)
+                                       window=s.window,
+                                       max_keys=step.max_kv_len if s.window is None else min(step.max_kv_len, s.window + step.max_q_len - 1))
             return
         ops.latent_attention_plain(q_lat, q, inv_freq, slot.kv, slot.table, step.seq_rows, step.token_seq,
                                    step.positions, self.sink, out_lat, heads=s.num_heads, head_dim=s.head_dim,

@@ -144,6 +144,7 @@ class RetentionMixer(Mixer):
     mean square, times ``silu(g)``; out projection (kernels: csrc/retention.cu).  The state is one
     32-bit ``[heads, head_dim, v_head_dim]`` row per request."""
     graph_safe = True
+    chunk_min_tokens = 16        # the longest entry of a step from which the chunked kernel runs; None: never
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
@@ -193,8 +194,12 @@ class RetentionMixer(Mixer):
         ops.retention_prep(proj, 0, self.qk, inv_freq, step.positions, q32, k32, heads=s.num_heads, head_dim=s.head_dim,
                            rotary_dim=rotary_dim, k_scale=s.head_dim ** -0.5)
         o = torch.empty(tokens, self.vv, dtype=torch.float32, device=dev)
-        ops.retention_scan(q32, k32, proj, 2 * self.qk, self._decay, slot.state, step, o, heads=s.num_heads,
-                           head_dim=s.head_dim, v_head_dim=s.v_head_dim)
+        # a step with a prompt portion takes the recurrence in chunks of 64 tokens (closed form per chunk);
+        # steps of single tokens and of short pieces walk it token by token
+        chunked = self.chunk_min_tokens is not None and step.max_q_len >= self.chunk_min_tokens
+        (ops.retention_chunk if chunked else ops.retention_scan)(
+            q32, k32, proj, 2 * self.qk, self._decay, slot.state, step, o, heads=s.num_heads, head_dim=s.head_dim,
+            v_head_dim=s.v_head_dim)
         gated = torch.empty(tokens, self.vv, dtype=x.dtype, device=dev)
         ops.retention_out(o, proj, 2 * self.qk + self.vv, gated, heads=s.num_heads, v_head_dim=s.v_head_dim, eps=s.norm_eps)
         return linear(gated, self.o)

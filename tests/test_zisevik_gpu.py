@@ -420,7 +420,54 @@ def test_tiled_latent_attention_against_the_kernel_per_token_and_head(rank, rot,
     ops.latent_attention_tiled(qfull, cache, table, seq_rows, cu_q, kv_len, sink, tiled, entries=entries, max_q_len=max(q_lens),
                                heads=heads, rank=rank, rot=rot, page_size=page, scale=scale, window=window)
     ops.error_check(dev)
-    diff = (tiled.float() - plain.float()).abs()
     assert bool(torch.isfinite(tiled.float()).all())
     # the rotated part of the query and the weights are rounded to bfloat16 in the tiled kernel only
+    diff = (tiled.float() - plain.float()).abs()
     assert float(diff.max()) < 3e-2 * float(plain.float().abs().max()), float(diff.max())
+    # the keys of a row tile dealt to several CTAs and merged: more splits than there are key tiles, too
+    max_keys = max(kv_lens) if window is None else min(max(kv_lens), window + max(q_lens) - 1)
+    for splits in (2, 3, 7):
+        split = torch.full((heads, tokens, rank), float("nan"), dtype=torch.bfloat16, device=dev)
+        ops.latent_attention_tiled(qfull, cache, table, seq_rows, cu_q, kv_len, sink, split, entries=entries, max_q_len=max(q_lens),
+                                   heads=heads, rank=rank, rot=rot, page_size=page, scale=scale, window=window, max_keys=max_keys,
+                                   splits=splits)
+        assert bool(torch.isfinite(split.float()).all())
+        assert float((split.float() - tiled.float()).abs().max()) < 1e-2 * float(plain.float().abs().max()), splits
+    ops.error_check(dev)
+
+
+@pytest.mark.parametrize("heads,d,dv,rot", [(3, 12, 20, 6), (2, 64, 64, 64), (1, 256, 40, 0), (4, 130, 33, 130)])
+def test_chunked_retention_against_the_walk_token_by_token(heads, d, dv, rot):
+    """The closed form per chunk of 64 tokens and the chain of single steps, on the same inputs and
+    from the same non-zero states: entries of 1, 63, 64, 65 and 200 tokens in one step, decays of 1,
+    just below 1 and 0.5; outputs and the states they leave."""
+    from types import SimpleNamespace
+    from sparseengine_b200.csrc import ops
+    dev = "cuda:0"
+    g = torch.Generator(device=dev).manual_seed(d + dv)
+    q_lens = [63, 1, 200, 64, 65]
+    tokens, entries = sum(q_lens), len(q_lens)
+    cu = [0]
+    for n in q_lens:
+        cu.append(cu[-1] + n)
+    step = SimpleNamespace(cu_q=torch.tensor(cu, dtype=torch.int32, device=dev), num_seqs=entries,
+                           seq_rows=torch.tensor([2, 0, 4, 1, 3], dtype=torch.int32, device=dev))
+    positions = torch.cat([torch.arange(500, 500 + n) for n in q_lens]).to(torch.int32).to(dev)
+    qk, vv = heads * d, heads * dv
+    for dtype in (torch.float32, torch.bfloat16):
+        proj = (torch.randn(tokens, 2 * qk + 2 * vv, generator=g, device=dev) * 0.5).to(dtype)
+        inv_freq = (10000.0 ** (-torch.arange(0, rot, 2, dtype=torch.float32) / max(rot, 1))).to(dev) if rot else None
+        q32, k32 = torch.empty(tokens, qk, device=dev), torch.empty(tokens, qk, device=dev)
+        ops.retention_prep(proj, 0, qk, inv_freq, positions, q32, k32, heads=heads, head_dim=d, rotary_dim=rot, k_scale=d ** -0.5)
+        decay = torch.tensor(([1.0, 0.9995, 0.5, 0.97] * heads)[:heads], dtype=torch.float32, device=dev)
+        state0 = torch.randn(5, heads * d * dv, generator=g, device=dev)
+        outs = []
+        for fn in (ops.retention_scan, ops.retention_chunk):
+            state = state0.clone()
+            o = torch.full((tokens, vv), float("nan"), device=dev)
+            fn(q32, k32, proj, 2 * qk, decay, state, step, o, heads=heads, head_dim=d, v_head_dim=dv)
+            outs.append((o, state))
+        (o1, s1), (o2, s2) = outs
+        assert bool(torch.isfinite(o2).all())
+        assert float((o1 - o2).abs().max()) < 2e-5 * float(o1.abs().max())
+        assert float((s1 - s2).abs().max()) < 2e-5 * float(s1.abs().max())
