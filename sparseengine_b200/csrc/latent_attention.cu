@@ -249,7 +249,10 @@ __global__ void latent_q_pack_kernel(const float* __restrict__ q_lat, const __nv
     }
 }
 
-template <int DMAX, int STAGES>
+// D16T, RT: the row's 16-dim groups rounded up to a multiple of four (the tile's chunks between the row's end and that
+// are zero-filled), and the same for the latent: loops of fixed length, no branch between the MMAs;
+// output columns beyond the latent are computed and dropped.
+template <int DMAX, int STAGES, int D16T, int RT>
 __global__ void __launch_bounds__(kThreads)
 latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __nv_bfloat16* __restrict__ cache,
                               const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
@@ -264,7 +267,8 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
     uint8_t* k_smem = lat_tile_smem + kTileRows * DMAX * 2;   // [STAGES][kTileKeys][DMAX]
     const int D = rank + rot;
     const int chunks = D / 8;                            // 16-byte chunks of a row
-    const int d16 = D / 16, r16 = rank / 16;
+    constexpr int kChunksT = 2 * D16T;                   // chunks the MMAs read; those beyond the row are zero
+    const int r16 = rank / 16;
 
     const int entry = blockIdx.y;
     const int tok0 = cu_q[entry];
@@ -307,24 +311,25 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
     {
         const __nv_bfloat16* src = qfull + ((size_t)tok0 * heads + row_base) * D;
         const int n_rows = min(kTileRows, total_rows - row_base);
-        for (int x = threadIdx.x; x < kTileRows * chunks; x += kThreads) {
-            const int r = x / chunks, c = x - r * chunks;
-            cp_async16(smem_u32(q_smem) + tile_off<DMAX>(r, c), src + (size_t)(r < n_rows ? r : 0) * D + c * 8, r < n_rows);
+        for (int x = threadIdx.x; x < kTileRows * kChunksT; x += kThreads) {
+            const int r = x / kChunksT, c = x % kChunksT;
+            const bool ok = r < n_rows && c < chunks;
+            cp_async16(smem_u32(q_smem) + tile_off<DMAX>(r, c), src + (size_t)(ok ? r : 0) * D + (ok ? c : 0) * 8, ok);
         }
     }
     auto load_tile = [&](int tile, int stage) {
         uint8_t* kbase = k_smem + (size_t)stage * kTileBytes;
         const int base = k_begin + tile * kTileKeys;
-        for (int x = threadIdx.x; x < kTileKeys * chunks; x += kThreads) {
-            const int r = x / chunks, c = x - r * chunks;
+        for (int x = threadIdx.x; x < kTileKeys * kChunksT; x += kThreads) {
+            const int r = x / kChunksT, c = x % kChunksT;
             const int j = base + r;
             // clamped into what every row of the tile may see: rows outside are zero-filled, never read (a
             // page behind the window may belong to another request by now)
             const int jj = min(max(j, k_lo), k_end - 1);
             const int page = row_table[jj / page_size];
-            const bool ok = page_in_pool(page, num_pages, error, 29) && j < k_end && j >= k_lo;
+            const bool ok = page_in_pool(page, num_pages, error, 29) && j < k_end && j >= k_lo && c < chunks;
             cp_async16(smem_u32(kbase) + tile_off<DMAX>(r, c),
-                       cache + ((size_t)(ok ? page : 0) * page_size + jj % page_size) * D + c * 8, ok);
+                       cache + ((size_t)(ok ? page : 0) * page_size + jj % page_size) * D + (ok ? c : 0) * 8, ok);
         }
     };
     for (int s = 0; s < STAGES - 1; ++s) {
@@ -332,9 +337,9 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
         cp_async_commit();                               // the first group also holds the query tile
     }
 
-    float o[DMAX / 8][4];
+    float o[2 * RT][4];
 #pragma unroll
-    for (int i = 0; i < DMAX / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    for (int i = 0; i < 2 * RT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     // the sink: a logit of its own (not scaled) that joins the maximum and the sum; in units of the
     // raw scores it is sink / scale
     float m_run[2], l_run[2];
@@ -362,8 +367,8 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
 #pragma unroll
         for (int n = 0; n < kTileKeys / 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
         const int mat = lane >> 3, rr = lane & 7;
-#pragma unroll 4
-        for (int kk = 0; kk < d16; ++kk) {
+#pragma unroll
+        for (int kk = 0; kk < D16T; ++kk) {
             uint32_t qa[4];
             ldmatrix_x4(qaddr + tile_off<DMAX>(warp * 16 + (mat & 1) * 8 + rr, 2 * kk + (mat >> 1)), qa[0], qa[1], qa[2], qa[3]);
 #pragma unroll
@@ -410,17 +415,18 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
 #pragma unroll
         for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * corr[h] + psum[h];
 #pragma unroll
-        for (int n2 = 0; n2 < DMAX / 16; ++n2) {
-            if (n2 < r16) {                              // the same for every thread
-                o[2 * n2][0] *= corr[0]; o[2 * n2][1] *= corr[0]; o[2 * n2][2] *= corr[1]; o[2 * n2][3] *= corr[1];
-                o[2 * n2 + 1][0] *= corr[0]; o[2 * n2 + 1][1] *= corr[0]; o[2 * n2 + 1][2] *= corr[1]; o[2 * n2 + 1][3] *= corr[1];
+        for (int i = 0; i < 2 * RT; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
 #pragma unroll
-                for (int kk = 0; kk < kTileKeys / 16; ++kk) {
-                    uint32_t b0, b1, b2, b3;
-                    ldmatrix_x4_trans(kaddr + tile_off<DMAX>(kk * 16 + (mat & 1) * 8 + rr, 2 * n2 + (mat >> 1)), b0, b1, b2, b3);
-                    mma_bf16(o[2 * n2], pa[kk], b0, b1);
-                    mma_bf16(o[2 * n2 + 1], pa[kk], b2, b3);
-                }
+        for (int kk = 0; kk < kTileKeys / 16; ++kk) {
+#pragma unroll
+            for (int n2 = 0; n2 < RT; ++n2) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(kaddr + tile_off<DMAX>(kk * 16 + (mat & 1) * 8 + rr, 2 * n2 + (mat >> 1)), b0, b1, b2, b3);
+                mma_bf16(o[2 * n2], pa[kk], b0, b1);
+                mma_bf16(o[2 * n2 + 1], pa[kk], b2, b3);
             }
         }
     }
@@ -439,7 +445,7 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
             if (t4 == 0) { part_ml[2 * at] = m_run[h]; part_ml[2 * at + 1] = l_run[h]; }
             float* dst = part_o + at * rank;
 #pragma unroll
-            for (int i = 0; i < DMAX / 8; ++i)
+            for (int i = 0; i < 2 * RT; ++i)
                 if (i < 2 * r16) *reinterpret_cast<float2*>(dst + i * 8 + 2 * t4) = make_float2(o[i][2 * h], o[i][2 * h + 1]);
         }
         return;
@@ -450,7 +456,7 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
         const float inv = 1.f / l_run[h];
         __nv_bfloat16* dst = out + ((size_t)head[h] * tokens + tok[h]) * rank;
 #pragma unroll
-        for (int i = 0; i < DMAX / 8; ++i)
+        for (int i = 0; i < 2 * RT; ++i)
             if (i < 2 * r16)
                 *reinterpret_cast<uint32_t*>(dst + i * 8 + 2 * t4) = pack_bf16(o[i][2 * h] * inv, o[i][2 * h + 1] * inv);
     }
@@ -480,7 +486,7 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
     }
 }
 
-template <int DMAX, int STAGES>
+template <int DMAX, int STAGES, int D16T, int RT>
 static int launch_tiled(const void* qfull, const void* cache, const int* table, int table_stride, const int* seq_rows,
                         const int* cu_q, const int* kv_len, const float* sink, void* out, int tokens, int entries,
                         int max_q_len, int heads, int rank, int rot, int page_size, float scale, int window, int num_pages,
@@ -488,7 +494,7 @@ static int launch_tiled(const void* qfull, const void* cache, const int* table, 
     const size_t smem = (size_t)(kTileRows + STAGES * kTileKeys) * DMAX * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(latent_attention_tiled_kernel<DMAX, STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(latent_attention_tiled_kernel<DMAX, STAGES, D16T, RT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
@@ -496,7 +502,7 @@ static int launch_tiled(const void* qfull, const void* cache, const int* table, 
     const long long row_tiles = ((long long)max_q_len * heads + kTileRows - 1) / kTileRows;
     if (row_tiles > 0x7fffffffLL || entries > 65535) return SE_ERR_UNSUPPORTED;
     dim3 grid((unsigned)row_tiles, entries, splits);
-    latent_attention_tiled_kernel<DMAX, STAGES><<<grid, kThreads, smem, stream>>>(
+    latent_attention_tiled_kernel<DMAX, STAGES, D16T, RT><<<grid, kThreads, smem, stream>>>(
         (const __nv_bfloat16*)qfull, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len, sink,
         (__nv_bfloat16*)out, tokens, heads, rank, rot, page_size, scale, window, num_pages, error, splits, tiles_per_split,
         part_o, part_ml);
@@ -538,11 +544,23 @@ extern "C" int se_latent_attention_tiled(const void* qfull, const void* cache, c
     if (!se_latent_attention_tiled_supported(rank, rot) || heads <= 0 || heads > 65535) return SE_ERR_UNSUPPORTED;
     if (!(scale > 0.f) || page_size <= 0 || splits < 1 || splits > 65535) return SE_ERR_ARGUMENT;
     if (splits > 1 && (tiles_per_split < 1 || part_o == nullptr || part_ml == nullptr)) return SE_ERR_ARGUMENT;
-    if (rank + rot <= 128)
-        return se::lat::launch_tiled<128, 3>(qfull, cache, table, table_stride, seq_rows, cu_q, kv_len, sink, out, tokens,
-                                             entries, max_q_len, heads, rank, rot, page_size, scale, window, num_pages,
-                                             error, splits, tiles_per_split, part_o, part_ml, stream);
-    return se::lat::launch_tiled<256, 2>(qfull, cache, table, table_stride, seq_rows, cu_q, kv_len, sink, out, tokens,
-                                         entries, max_q_len, heads, rank, rot, page_size, scale, window, num_pages, error,
-                                         splits, tiles_per_split, part_o, part_ml, stream);
+    const int d16t = (rank + rot + 63) / 64 * 4, rt = (rank + 63) / 64 * 4;
+#define SE_LAT_TILED(DMAX, STAGES, D16T, RT)                                                                          \
+    if (d16t == D16T && rt == RT)                                                                                     \
+        return se::lat::launch_tiled<DMAX, STAGES, D16T, RT>(qfull, cache, table, table_stride, seq_rows, cu_q, kv_len, \
+                                                             sink, out, tokens, entries, max_q_len, heads, rank, rot,   \
+                                                             page_size, scale, window, num_pages, error, splits,       \
+                                                             tiles_per_split, part_o, part_ml, stream)
+    SE_LAT_TILED(128, 3, 4, 4);
+    SE_LAT_TILED(128, 3, 8, 4);
+    SE_LAT_TILED(128, 3, 8, 8);
+    SE_LAT_TILED(256, 2, 12, 4);
+    SE_LAT_TILED(256, 2, 12, 8);
+    SE_LAT_TILED(256, 2, 12, 12);
+    SE_LAT_TILED(256, 2, 16, 4);
+    SE_LAT_TILED(256, 2, 16, 8);
+    SE_LAT_TILED(256, 2, 16, 12);
+    SE_LAT_TILED(256, 2, 16, 16);
+#undef SE_LAT_TILED
+    return SE_ERR_UNSUPPORTED;
 }
