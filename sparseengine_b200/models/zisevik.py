@@ -31,7 +31,7 @@ ARCHITECTURE = "Zisevik"
 MIXER_TYPES = ("latent_attention", "retention")
 DEFAULT_MAX_POSITION = 1 << 20      # the design has no position table; the cache manager wants a bound
 
-_MIXER_KEYS = {"latent_attention": ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank", "scale"),
+_MIXER_KEYS = {"latent_attention": ("heads", "dim", "rot_dim", "vdim", "q_rank", "kv_rank"),
                "retention": ("heads", "dim", "vdim", "decay")}
 
 
@@ -105,7 +105,7 @@ def _latent_attention(cfg, m, p):
     q_rank, rank = int(m["q_rank"]), int(m["kv_rank"])
     window = (m.get("mask") or {}).get("size")
     spec = LatentAttentionSpec(hidden_size=cfg.width, num_heads=H, head_dim=d, rot_dim=r, v_head_dim=dv, q_rank=q_rank,
-                               kv_rank=rank, scale=float(m["scale"]), window=int(window) if window else None, sink=True,
+                               kv_rank=rank, scale=float(m.get("scale", (d + r) ** -0.5)), window=int(window) if window else None, sink=True,
                                position=_rotary(m, r), norm_eps=cfg.norm_eps)
     sources = {"mixer.down": (Source(p + "dq", ((0, q_rank),)), Source(p + "dkv", ((q_rank, rank + r),))),
                "mixer.q_norm": (Source(p + "dq.norm"),), "mixer.kv_norm": (Source(p + "dkv.norm"),),

@@ -64,3 +64,22 @@ def test_what_a_configuration_must_have():
         breaker(bad)
         with pytest.raises(ValueError, match=word):
             load_model_spec(bad)
+
+
+def test_sizes_the_kernels_do_not_take_are_refused_when_the_parts_are_built():
+    from sparseengine_b200.config.specs import LatentAttentionSpec, RetentionSpec, RotarySpec
+    from sparseengine_b200.csrc import ops
+    from sparseengine_b200.parts.base import make_mixer
+    rot = RotarySpec(rotary_dim=16, theta=1e4)
+    ok = dict(hidden_size=64, num_heads=2, head_dim=16, rot_dim=16, v_head_dim=16, q_rank=8, scale=0.1, position=rot)
+    make_mixer(LatentAttentionSpec(kv_rank=ops.LIMITS["latent_max_row"] - 16, **ok), torch.float32)
+    with pytest.raises(ValueError, match=str(ops.LIMITS["latent_max_row"])):
+        make_mixer(LatentAttentionSpec(kv_rank=ops.LIMITS["latent_max_row"] - 15, **ok), torch.float32)
+    with pytest.raises(ValueError, match="rotates 16 dims"):
+        make_mixer(LatentAttentionSpec(kv_rank=8, **dict(ok, rot_dim=8)), torch.float32)
+    most = ops.LIMITS["retention_max_head_dim"]
+    make_mixer(RetentionSpec(hidden_size=64, num_heads=2, head_dim=most, v_head_dim=8, decays=(0.9, 0.8), position=rot), torch.float32)
+    with pytest.raises(ValueError, match=str(most)):
+        make_mixer(RetentionSpec(hidden_size=64, num_heads=2, head_dim=most + 1, v_head_dim=8, decays=(0.9, 0.8)), torch.float32)
+    with pytest.raises(ValueError, match="one decay per head"):
+        make_mixer(RetentionSpec(hidden_size=64, num_heads=2, head_dim=8, v_head_dim=8, decays=(0.9,)), torch.float32)
