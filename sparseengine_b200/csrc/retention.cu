@@ -135,6 +135,11 @@ retention_scan_kernel(const float* __restrict__ q32, const float* __restrict__ k
 constexpr int kChunk = 64;
 constexpr int kChunkThreads = 256;
 
+// a 4-byte asynchronous copy into shared memory: a chunk's q and k are all asked for before any of them is waited for
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
 __device__ __forceinline__ int swz(int i, int t) { return i * kChunk + ((((t >> 2) ^ (i & 15)) << 2) | (t & 3)); }
 
 template <typename T>
@@ -166,19 +171,27 @@ retention_chunk_kernel(const float* __restrict__ q32, const float* __restrict__ 
         for (int x = threadIdx.x; x < kChunk * d; x += kChunkThreads) {
             const int t = x / d, i = x - t * d;
             const size_t at = ((size_t)(tb + t) * heads + h) * d + i;
-            qs[swz(i, t)] = t < n ? q32[at] : 0.f;
-            ks[swz(i, t)] = t < n ? k32[at] : 0.f;
+            if (t < n) {
+                cp_async4(qs + swz(i, t), q32 + at);
+                cp_async4(ks + swz(i, t), k32 + at);
+            } else {
+                qs[swz(i, t)] = 0.f;
+                ks[swz(i, t)] = 0.f;
+            }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
         for (int x = threadIdx.x; x < kChunk * 32; x += kChunkThreads) {
             const int t = x >> 5, c = x & 31;
             vs[x] = (t < n && c0 + c < dv) ? to_float(proj[(size_t)(tb + t) * proj_stride + v_off + h * dv + c0 + c]) : 0.f;
         }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         // scores of the chunk with their decays: a 4 x 4 tile per thread, tiles above the diagonal are zero
         {
             const int tt = (threadIdx.x >> 4) * 4, ss = (threadIdx.x & 15) * 4;
             float acc[4][4] = {};
             if (ss <= tt + 3) {
+#pragma unroll 4
                 for (int i = 0; i < d; ++i) {
                     const float4 qv = *reinterpret_cast<const float4*>(qs + swz(i, tt));
                     const float4 kv = *reinterpret_cast<const float4*>(ks + swz(i, ss));
@@ -214,6 +227,7 @@ retention_chunk_kernel(const float* __restrict__ q32, const float* __restrict__ 
                 acc[0] += a0.x * v; acc[1] += a0.y * v; acc[2] += a0.z * v; acc[3] += a0.w * v;
                 acc[4] += a1.x * v; acc[5] += a1.y * v; acc[6] += a1.z * v; acc[7] += a1.w * v;
             }
+#pragma unroll 4
             for (int i = 0; i < d; ++i) {
                 const float4 q0 = *reinterpret_cast<const float4*>(qs + swz(i, tg));
                 const float4 q1 = *reinterpret_cast<const float4*>(qs + swz(i, tg + 4));
