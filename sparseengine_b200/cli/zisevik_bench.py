@@ -26,10 +26,11 @@ WINDOW = 1024
 
 
 def zisevik_config(width: int) -> dict:
-    """Four layers, the first two run three times (eight visits: three retention, five latent
-    attention).  Latent attention: heads of 64 + 64 (rotated) query/key dims, values of 64, a cached
-    row of 192 + 64, a window of 1,024; retention: heads with a 128 x 128 state; feed-forwards:
-    dense of 4 x width, or 8 experts of width each, 2 per token."""
+    """Four layers, the two in the middle run three times (eight visits: five latent attention,
+    three retention; six dense and two routed feed-forwards).  Latent attention: heads of 64 + 64
+    (rotated) query/key dims, values of 64, a cached row of 192 + 64, a window of 1,024; retention:
+    heads with a 128 x 128 state; feed-forwards: dense of 4 x width, or 8 experts of width each, 2 per
+    token."""
     heads = width // 128
     lat = {"heads": 2 * heads, "dim": 64, "rot_dim": 64, "vdim": 64, "q_rank": width // 2, "kv_rank": 192,
            "mask": {"size": WINDOW}, "rot": {"base": 500000.0, "dims": 64}, "scale": 128 ** -0.5}
@@ -37,9 +38,9 @@ def zisevik_config(width: int) -> dict:
            "decay": [1.0 - 2.0 ** (-5 - 7 * i / max(1, heads - 1)) for i in range(heads)]}
     dense = {"kind": "dense", "ff": 4 * width}
     moe = {"kind": "moe", "expert": {"ff": width}, "router": {"experts": 8, "top": 2}}
-    layers = [{"type": "retention", "mixer": ret, "mlp": dense}, {"type": "latent_attention", "mixer": dict(lat), "mlp": moe},
+    layers = [{"type": "latent_attention", "mixer": dict(lat), "mlp": moe}, {"type": "retention", "mixer": ret, "mlp": dense},
               {"type": "latent_attention", "mixer": dict(lat), "mlp": dense}, {"type": "latent_attention", "mixer": dict(lat), "mlp": moe}]
-    return {"architecture": "Zisevik", "vocab": VOCAB, "width": width, "layers": layers, "loop": {"start": 0, "stop": 2, "times": 3},
+    return {"architecture": "Zisevik", "vocab": VOCAB, "width": width, "layers": layers, "loop": {"start": 1, "stop": 3, "times": 3},
             "norm": {"eps": 1e-6}, "max_position": 16384}
 
 
@@ -53,7 +54,7 @@ def _kernels(width: int, cases, pk: dict) -> dict:
     from ..csrc import ops
     dev = torch.device("cuda:0")
     cfg = zisevik_config(width)
-    lat, ret = cfg["layers"][1]["mixer"], cfg["layers"][0]["mixer"]
+    lat, ret = cfg["layers"][0]["mixer"], cfg["layers"][1]["mixer"]
     bf = torch.bfloat16
     out = {}
     for tokens, entries, held in cases:
