@@ -216,7 +216,9 @@ extern "C" int se_latent_attention_plain(const float* q_lat, const void* q, int 
 namespace se {
 namespace lat {
 
-constexpr int kTileKeys = 64;
+// Tiles of 64 rows; 64 keys for steps of single tokens, 32 keys for steps with prompt portions (fewer score and weight
+// registers leave the compiler room to ask for the next fragments while the MMAs of these run: 198 -> 181 us over a
+// 2,048-token prompt; three CTAs per SM at 168 registers did not pay, nor did a second set of score accumulators).
 constexpr int kTileRows = 64;
 constexpr int kWarps = 4;
 constexpr int kThreads = 32 * kWarps;
@@ -252,8 +254,8 @@ __global__ void latent_q_pack_kernel(const float* __restrict__ q_lat, const __nv
 // D16T, RT: the row's 16-dim groups rounded up to a multiple of four (the tile's chunks between the row's end and that
 // are zero-filled), and the same for the latent: loops of fixed length, no branch between the MMAs;
 // output columns beyond the latent are computed and dropped.
-template <int DMAX, int STAGES, int D16T, int RT>
-__global__ void __launch_bounds__(kThreads)
+template <int DMAX, int STAGES, int D16T, int RT, int TK, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
 latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __nv_bfloat16* __restrict__ cache,
                               const int* __restrict__ table, int table_stride, const int* __restrict__ seq_rows,
                               const int* __restrict__ cu_q, const int* __restrict__ kv_len,
@@ -261,6 +263,7 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
                               int rank, int rot, int page_size, float scale, int window, int num_pages,
                               int* __restrict__ error, int splits, int tiles_per_split, float* __restrict__ part_o,
                               float* __restrict__ part_ml) {
+    constexpr int kTileKeys = TK;
     constexpr int kTileBytes = kTileKeys * DMAX * 2;
     extern __shared__ __align__(128) uint8_t lat_tile_smem[];
     uint8_t* q_smem = lat_tile_smem;                     // [kTileRows][DMAX]
@@ -317,19 +320,24 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
             cp_async16(smem_u32(q_smem) + tile_off<DMAX>(r, c), src + (size_t)(ok ? r : 0) * D + (ok ? c : 0) * 8, ok);
         }
     }
+    // A key row is copied by kThreads / kTileKeys neighbouring threads, 16 bytes each in turn: one block-table lookup
+    // per thread and tile, and the threads of a row ask for adjacent bytes.
+    constexpr int kPerRow = kThreads / kTileKeys;
+    const int ld_row = threadIdx.x / kPerRow, ld_c0 = threadIdx.x % kPerRow;
     auto load_tile = [&](int tile, int stage) {
         uint8_t* kbase = k_smem + (size_t)stage * kTileBytes;
-        const int base = k_begin + tile * kTileKeys;
-        for (int x = threadIdx.x; x < kTileKeys * kChunksT; x += kThreads) {
-            const int r = x / kChunksT, c = x % kChunksT;
-            const int j = base + r;
-            // clamped into what every row of the tile may see: rows outside are zero-filled, never read (a
-            // page behind the window may belong to another request by now)
-            const int jj = min(max(j, k_lo), k_end - 1);
-            const int page = row_table[jj / page_size];
-            const bool ok = page_in_pool(page, num_pages, error, 29) && j < k_end && j >= k_lo && c < chunks;
-            cp_async16(smem_u32(kbase) + tile_off<DMAX>(r, c),
-                       cache + ((size_t)(ok ? page : 0) * page_size + jj % page_size) * D + (ok ? c : 0) * 8, ok);
+        const int j = k_begin + tile * kTileKeys + ld_row;
+        // clamped into what every row of the tile may see: rows outside are zero-filled, never read (a
+        // page behind the window may belong to another request by now)
+        const int jj = min(max(j, k_lo), k_end - 1);
+        const int page = row_table[jj / page_size];
+        const bool row_ok = page_in_pool(page, num_pages, error, 29) && j < k_end && j >= k_lo;
+        const __nv_bfloat16* src = cache + ((size_t)(row_ok ? page : 0) * page_size + jj % page_size) * D;
+        const uint32_t dst = smem_u32(kbase);
+#pragma unroll
+        for (int c = ld_c0; c < kChunksT; c += kPerRow) {
+            const bool ok = row_ok && c < chunks;
+            cp_async16(dst + tile_off<DMAX>(ld_row, c), src + (ok ? c : 0) * 8, ok);
         }
     };
     for (int s = 0; s < STAGES - 1; ++s) {
@@ -351,6 +359,8 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
     const float scale_log2 = scale * 1.4426950408889634f;
     const int warp_last_row = min(row_base + warp * 16 + 15, total_rows - 1);
     const int warp_max_pos = q_start + warp_last_row / heads;
+    const int warp_min_pos = q_start + min(row_base + warp * 16, total_rows - 1) / heads;
+    const int warp_max_lo = window > 0 ? max(0, warp_max_pos - window + 1) : 0;
     const uint32_t qaddr = smem_u32(q_smem);
 
     for (int tile = t_begin; tile < t_end; ++tile) {
@@ -380,15 +390,24 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
             }
         }
         float mx[2] = {-INFINITY, -INFINITY};
+        // a tile that every row of the warp sees whole (most tiles of a long window) needs no mask
+        if (key0 >= warp_max_lo && key0 + kTileKeys - 1 <= warp_min_pos) {
 #pragma unroll
-        for (int n = 0; n < kTileKeys / 8; ++n)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int j = key0 + n * 8 + 2 * t4 + (e & 1);
-                const int h = e >> 1;
-                if (j > pos[h] || j < lo[h]) s[n][e] = -INFINITY;
-                mx[h] = fmaxf(mx[h], s[n][e]);
+            for (int n = 0; n < kTileKeys / 8; ++n) {
+                mx[0] = fmaxf(mx[0], fmaxf(s[n][0], s[n][1]));
+                mx[1] = fmaxf(mx[1], fmaxf(s[n][2], s[n][3]));
             }
+        } else {
+#pragma unroll
+            for (int n = 0; n < kTileKeys / 8; ++n)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = key0 + n * 8 + 2 * t4 + (e & 1);
+                    const int h = e >> 1;
+                    if (j > pos[h] || j < lo[h]) s[n][e] = -INFINITY;
+                    mx[h] = fmaxf(mx[h], s[n][e]);
+                }
+        }
         float corr[2], m_use[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
@@ -414,10 +433,12 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
         }
 #pragma unroll
         for (int h = 0; h < 2; ++h) l_run[h] = l_run[h] * corr[h] + psum[h];
+        if (__any_sync(0xffffffffu, corr[0] != 1.f || corr[1] != 1.f)) {      // the running maxima mostly stand still
 #pragma unroll
-        for (int i = 0; i < 2 * RT; ++i) {
-            o[i][0] *= corr[0]; o[i][1] *= corr[0];
-            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            for (int i = 0; i < 2 * RT; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
         }
 #pragma unroll
         for (int kk = 0; kk < kTileKeys / 16; ++kk) {
@@ -486,15 +507,15 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
     }
 }
 
-template <int DMAX, int STAGES, int D16T, int RT>
+template <int DMAX, int STAGES, int D16T, int RT, int TK, int MINB>
 static int launch_tiled(const void* qfull, const void* cache, const int* table, int table_stride, const int* seq_rows,
                         const int* cu_q, const int* kv_len, const float* sink, void* out, int tokens, int entries,
                         int max_q_len, int heads, int rank, int rot, int page_size, float scale, int window, int num_pages,
                         int* error, int splits, int tiles_per_split, float* part_o, float* part_ml, cudaStream_t stream) {
-    const size_t smem = (size_t)(kTileRows + STAGES * kTileKeys) * DMAX * 2;
+    const size_t smem = (size_t)(kTileRows + STAGES * TK) * DMAX * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(latent_attention_tiled_kernel<DMAX, STAGES, D16T, RT>,
+        cudaError_t e = cudaFuncSetAttribute(latent_attention_tiled_kernel<DMAX, STAGES, D16T, RT, TK, MINB>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
@@ -502,7 +523,7 @@ static int launch_tiled(const void* qfull, const void* cache, const int* table, 
     const long long row_tiles = ((long long)max_q_len * heads + kTileRows - 1) / kTileRows;
     if (row_tiles > 0x7fffffffLL || entries > 65535) return SE_ERR_UNSUPPORTED;
     dim3 grid((unsigned)row_tiles, entries, splits);
-    latent_attention_tiled_kernel<DMAX, STAGES, D16T, RT><<<grid, kThreads, smem, stream>>>(
+    latent_attention_tiled_kernel<DMAX, STAGES, D16T, RT, TK, MINB><<<grid, kThreads, smem, stream>>>(
         (const __nv_bfloat16*)qfull, (const __nv_bfloat16*)cache, table, table_stride, seq_rows, cu_q, kv_len, sink,
         (__nv_bfloat16*)out, tokens, heads, rank, rot, page_size, scale, window, num_pages, error, splits, tiles_per_split,
         part_o, part_ml);
@@ -539,18 +560,20 @@ extern "C" int se_latent_attention_tiled(const void* qfull, const void* cache, c
                                          const int* seq_rows, const int* cu_q, const int* kv_len, const float* sink,
                                          void* out, int tokens, int entries, int max_q_len, int heads, int rank, int rot,
                                          int page_size, float scale, int window, int num_pages, int* error, int splits,
-                                         int tiles_per_split, float* part_o, float* part_ml, cudaStream_t stream) {
+                                         int tiles_per_split, float* part_o, float* part_ml, int tile_keys,
+                                         cudaStream_t stream) {
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (!se_latent_attention_tiled_supported(rank, rot) || heads <= 0 || heads > 65535) return SE_ERR_UNSUPPORTED;
     if (!(scale > 0.f) || page_size <= 0 || splits < 1 || splits > 65535) return SE_ERR_ARGUMENT;
     if (splits > 1 && (tiles_per_split < 1 || part_o == nullptr || part_ml == nullptr)) return SE_ERR_ARGUMENT;
+    if (tile_keys != 64 && tile_keys != 32) return SE_ERR_ARGUMENT;
     const int d16t = (rank + rot + 63) / 64 * 4, rt = (rank + 63) / 64 * 4;
+#define SE_LAT_ARGS qfull, cache, table, table_stride, seq_rows, cu_q, kv_len, sink, out, tokens, entries, max_q_len, heads, \
+                    rank, rot, page_size, scale, window, num_pages, error, splits, tiles_per_split, part_o, part_ml, stream
 #define SE_LAT_TILED(DMAX, STAGES, D16T, RT)                                                                          \
     if (d16t == D16T && rt == RT)                                                                                     \
-        return se::lat::launch_tiled<DMAX, STAGES, D16T, RT>(qfull, cache, table, table_stride, seq_rows, cu_q, kv_len, \
-                                                             sink, out, tokens, entries, max_q_len, heads, rank, rot,   \
-                                                             page_size, scale, window, num_pages, error, splits,       \
-                                                             tiles_per_split, part_o, part_ml, stream)
+        return tile_keys == 64 ? se::lat::launch_tiled<DMAX, STAGES, D16T, RT, 64, 1>(SE_LAT_ARGS)                     \
+                               : se::lat::launch_tiled<DMAX, 3, D16T, RT, 32, 2>(SE_LAT_ARGS)
     SE_LAT_TILED(128, 3, 4, 4);
     SE_LAT_TILED(128, 3, 8, 4);
     SE_LAT_TILED(128, 3, 8, 8);
@@ -562,5 +585,6 @@ extern "C" int se_latent_attention_tiled(const void* qfull, const void* cache, c
     SE_LAT_TILED(256, 2, 16, 12);
     SE_LAT_TILED(256, 2, 16, 16);
 #undef SE_LAT_TILED
+#undef SE_LAT_ARGS
     return SE_ERR_UNSUPPORTED;
 }

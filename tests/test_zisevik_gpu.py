@@ -426,13 +426,14 @@ def test_tiled_latent_attention_against_the_kernel_per_token_and_head(rank, rot,
     assert float(diff.max()) < 3e-2 * float(plain.float().abs().max()), float(diff.max())
     # the keys of a row tile dealt to several CTAs and merged: more splits than there are key tiles, too
     max_keys = max(kv_lens) if window is None else min(max(kv_lens), window + max(q_lens) - 1)
-    for splits in (2, 3, 7):
+    # ... with key tiles of 64 and of 32
+    for splits, tile_keys in ((2, 64), (3, 64), (7, 64), (1, 32), (2, 32), (5, 32), (1, 64)):
         split = torch.full((heads, tokens, rank), float("nan"), dtype=torch.bfloat16, device=dev)
         ops.latent_attention_tiled(qfull, cache, table, seq_rows, cu_q, kv_len, sink, split, entries=entries, max_q_len=max(q_lens),
                                    heads=heads, rank=rank, rot=rot, page_size=page, scale=scale, window=window, max_keys=max_keys,
-                                   splits=splits)
-        assert bool(torch.isfinite(split.float()).all())
-        assert float((split.float() - tiled.float()).abs().max()) < 1e-2 * float(plain.float().abs().max()), splits
+                                   splits=splits, tile_keys=tile_keys)
+        assert bool(torch.isfinite(split.float()).all()), (splits, tile_keys)
+        assert float((split.float() - tiled.float()).abs().max()) < 1e-2 * float(plain.float().abs().max()), (splits, tile_keys)
     ops.error_check(dev)
 
 
