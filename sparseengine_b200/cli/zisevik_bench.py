@@ -101,7 +101,7 @@ def _kernels(width: int, cases, pk: dict) -> dict:
         add("latent_q_pack", lambda: ops.latent_q_pack(q_lat, q, inv, step.positions, qfull, heads=H, head_dim=d, rank=rank, rot=r,
                                                        rotary_dim=r), tokens * H * (rank * 4 + r * 2 + D * 2))
         sink = torch.zeros(H, device=dev)
-        o_lat = torch.empty(H, tokens, rank, device=dev, dtype=bf)
+        o_lat = torch.empty(tokens, H, rank, device=dev, dtype=bf)
         # keys a query sees: min(window, position + 1)
         seen = sum(min(WINDOW, held + i + 1) for i in range(per)) * entries
         key_rows = entries * min(held + per, WINDOW + per - 1)

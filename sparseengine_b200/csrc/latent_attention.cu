@@ -70,7 +70,7 @@ constexpr int kLatWarps = 4;
 
 // One block per (token, head); a warp takes every fourth key, lane l the dims l, l + 32, ...
 // q_lat: float [heads, tokens, rank]; q: [tokens, heads * (d + rot)] in the activation type, of which
-// the last `rot` of each head are the rotated part (rotated here); out: [heads, tokens, rank].
+// the last `rot` of each head are the rotated part (rotated here); out: [tokens, heads, rank].
 template <typename T, int NL>
 __global__ void latent_attention_plain_kernel(const float* __restrict__ q_lat, const T* __restrict__ q, int d,
                                               const float* __restrict__ inv_freq, int rotary_dim,
@@ -148,7 +148,7 @@ __global__ void latent_attention_plain_kernel(const float* __restrict__ q_lat, c
     float lt = sink != nullptr ? expf(sk - mt) : 0.f;
 #pragma unroll
     for (int w = 0; w < kLatWarps; ++w) lt += sm[w] == -INFINITY ? 0.f : sl[w] * expf(sm[w] - mt);
-    T* op = out + ((size_t)h * tokens + t) * rank;
+    T* op = out + ((size_t)t * heads + h) * rank;
     for (int dim = threadIdx.x; dim < rank; dim += blockDim.x) {
         float o = 0.f;
 #pragma unroll
@@ -159,7 +159,7 @@ __global__ void latent_attention_plain_kernel(const float* __restrict__ q_lat, c
 
 }  // namespace se
 
-extern "C" int se_latent_max_row() { return 32 * 20; }
+extern "C" int se_latent_max_row() { return 32 * 32; }
 
 extern "C" int se_latent_prep(const void* proj, int proj_stride, const void* q_w, const void* kv_w, const float* inv_freq,
                               const int* positions, const int* token_seq, const int* seq_rows, const int* table,
@@ -194,7 +194,8 @@ extern "C" int se_latent_attention_plain(const float* q_lat, const void* q, int 
     SE_DISPATCH_DTYPE(dtype, T, {
         if (D <= 128) SE_LAT_LAUNCH(4);
         else if (D <= 256) SE_LAT_LAUNCH(8);
-        else SE_LAT_LAUNCH(20);
+        else if (D <= 640) SE_LAT_LAUNCH(20);
+        else SE_LAT_LAUNCH(32);
     });
 #undef SE_LAT_LAUNCH
     SE_LAUNCH_CHECK();
@@ -475,7 +476,7 @@ latent_attention_tiled_kernel(const __nv_bfloat16* __restrict__ qfull, const __n
     for (int h = 0; h < 2; ++h) {
         if (!valid[h]) continue;
         const float inv = 1.f / l_run[h];
-        __nv_bfloat16* dst = out + ((size_t)head[h] * tokens + tok[h]) * rank;
+        __nv_bfloat16* dst = out + ((size_t)tok[h] * heads + head[h]) * rank;
 #pragma unroll
         for (int i = 0; i < 2 * RT; ++i)
             if (i < 2 * r16)
@@ -503,7 +504,7 @@ __global__ void latent_attention_merge_kernel(const float* __restrict__ part_o, 
             const float m = part_ml[2 * (at + z)];
             if (m != -INFINITY) o += part_o[(at + z) * rank + c] * exp2f((m - mt) * scale_log2);
         }
-        out[((size_t)h * tokens + t) * rank + c] = __float2bfloat16_rn(o / lt);
+        out[((size_t)t * heads + h) * rank + c] = __float2bfloat16_rn(o / lt);
     }
 }
 
@@ -551,7 +552,7 @@ extern "C" int se_latent_q_pack(const float* q_lat, const void* q, int d, const 
     SE_LAUNCH_CHECK();
 }
 
-// qfull: bfloat16 [tokens, heads, rank + rot]; out: bfloat16 [heads, tokens, rank]; cu_q: [entries + 1]
+// qfull: bfloat16 [tokens, heads, rank + rot]; out: bfloat16 [tokens, heads, rank]; cu_q: [entries + 1]
 // token offsets; kv_len: [entries] keys of each request once this step's rows are written.
 // splits > 1: the key tiles a row tile sees are dealt to `splits` CTAs, `tiles_per_split` tiles of 64 keys
 // each (steps of few rows over long windows); part_o: float [tokens * heads * splits * rank], part_ml:

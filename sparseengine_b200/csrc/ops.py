@@ -47,7 +47,7 @@ LIMITS = {
     "attention_max_head_dim": 256,          # in steps of 16
     "layernorm_max_width": 51200,           # as the RMS norm: the row is kept in shared memory in 32-bit
     "recurrent_max_state_rows": 512,        # rows of a recurrence's state on the key/state side (16 registers x 32 lanes)
-    "latent_max_row": 640,                  # latent plus shared key part of one position (20 registers x 32 lanes)
+    "latent_max_row": 1024,                 # latent plus shared key part of one position (32 registers x 32 lanes)
     "retention_max_head_dim": 256,          # rows of a retention state (32 registers x 8 warps)
     "grid_dim_yz": 65535,                   # heads, KV heads and a step's entries map to grid dimensions y and z
 }
@@ -302,7 +302,7 @@ def latent_prep(proj, q_w, kv_w, inv_freq, positions, token_seq, seq_rows, table
 def latent_attention_plain(q_lat, q, inv_freq, cache, table, seq_rows, token_seq, positions, sink, out, *, heads,
                            head_dim, rank, rot, rotary_dim, page_size, scale, window=None, num_pages=None):
     """``q_lat`` float32 [heads, tokens, rank] (queries taken into the latent's space), ``q`` [tokens,
-    heads * (head_dim + rot)] whose rotated parts are rotated here; ``out`` [heads, tokens, rank]."""
+    heads * (head_dim + rot)] whose rotated parts are rotated here; ``out`` [tokens, heads, rank]."""
     tokens = q.shape[0]
     dt = q.dtype
     _check(_fn("se_latent_attention_plain", "ppipi" "ppi" "pppp" "p" "iiii" "i" "f" "ii" "p" "ip")(
@@ -359,7 +359,7 @@ def latent_split_plan(row_tiles: int, entries: int, max_keys: int, sms: Optional
 
 def latent_attention_tiled(qfull, cache, table, seq_rows, cu_q, kv_len, sink, out, *, entries, max_q_len, heads, rank, rot,
                            page_size, scale, window=None, num_pages=None, max_keys=None, splits=None, tile_keys=None):
-    """bfloat16, tensor-core tiles; ``qfull`` [tokens, heads, rank + rot], ``out`` [heads, tokens, rank].
+    """bfloat16, tensor-core tiles; ``qfull`` [tokens, heads, rank + rot], ``out`` [tokens, heads, rank].
     ``max_keys``: an upper bound of the keys a query of this step sees (window, or the longest
     request); with it, steps of few rows are split along the keys (``splits`` forces a count)."""
     tokens = qfull.shape[0]

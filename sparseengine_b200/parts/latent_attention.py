@@ -88,10 +88,12 @@ class LatentAttention(Mixer):
         q_plain = q.view(tokens, H, d + r)[:, :, :d].transpose(0, 1)
         q_lat = torch.bmm(q_plain, self.uk.view(H, d, rank), out_dtype=torch.float32) if x.dtype != torch.float32 \
             else torch.bmm(q_plain, self.uk.view(H, d, rank))
-        out_lat = torch.empty(H, tokens, rank, dtype=x.dtype, device=dev)
+        out_lat = torch.empty(tokens, H, rank, dtype=x.dtype, device=dev)
         self.attend(q_lat, q, inv_freq, rotary_dim, out_lat, step, slot)
-        heads_out = torch.bmm(out_lat, self.uv.view(H, s.v_head_dim, rank).transpose(1, 2))      # [H, tokens, dv]
-        return linear(heads_out.transpose(0, 1).reshape(tokens, H * s.v_head_dim), self.o)
+        # the values' up-projection per head, read from and written to token-major rows through strided views
+        heads_out = torch.empty(tokens, H, s.v_head_dim, dtype=x.dtype, device=dev)
+        torch.bmm(out_lat.transpose(0, 1), self.uv.view(H, s.v_head_dim, rank).transpose(1, 2), out=heads_out.transpose(0, 1))
+        return linear(heads_out.view(tokens, H * s.v_head_dim), self.o)
 
     use_tensor_cores = None      # False: always the kernel with one block per (token, head)
 

@@ -411,12 +411,12 @@ def test_tiled_latent_attention_against_the_kernel_per_token_and_head(rank, rot,
     inv_freq = (10000.0 ** (-torch.arange(0, rot, 2, dtype=torch.float32) / max(rot, 1))).to(dev) if rot else None
     sink = torch.linspace(-6.0, 4.0, heads, device=dev)
     scale = D ** -0.5 * 2.0
-    plain = torch.empty(heads, tokens, rank, dtype=torch.bfloat16, device=dev)
+    plain = torch.empty(tokens, heads, rank, dtype=torch.bfloat16, device=dev)
     ops.latent_attention_plain(q_lat, q, inv_freq, cache, table, seq_rows, token_seq, positions, sink, plain, heads=heads,
                                head_dim=d, rank=rank, rot=rot, rotary_dim=rot, page_size=page, scale=scale, window=window)
     qfull = torch.empty(tokens, heads, D, dtype=torch.bfloat16, device=dev)
     ops.latent_q_pack(q_lat, q, inv_freq, positions, qfull, heads=heads, head_dim=d, rank=rank, rot=rot, rotary_dim=rot)
-    tiled = torch.full((heads, tokens, rank), float("nan"), dtype=torch.bfloat16, device=dev)
+    tiled = torch.full((tokens, heads, rank), float("nan"), dtype=torch.bfloat16, device=dev)
     ops.latent_attention_tiled(qfull, cache, table, seq_rows, cu_q, kv_len, sink, tiled, entries=entries, max_q_len=max(q_lens),
                                heads=heads, rank=rank, rot=rot, page_size=page, scale=scale, window=window)
     ops.error_check(dev)
@@ -428,7 +428,7 @@ def test_tiled_latent_attention_against_the_kernel_per_token_and_head(rank, rot,
     max_keys = max(kv_lens) if window is None else min(max(kv_lens), window + max(q_lens) - 1)
     # ... with key tiles of 64 and of 32
     for splits, tile_keys in ((2, 64), (3, 64), (7, 64), (1, 32), (2, 32), (5, 32), (1, 64)):
-        split = torch.full((heads, tokens, rank), float("nan"), dtype=torch.bfloat16, device=dev)
+        split = torch.full((tokens, heads, rank), float("nan"), dtype=torch.bfloat16, device=dev)
         ops.latent_attention_tiled(qfull, cache, table, seq_rows, cu_q, kv_len, sink, split, entries=entries, max_q_len=max(q_lens),
                                    heads=heads, rank=rank, rot=rot, page_size=page, scale=scale, window=window, max_keys=max_keys,
                                    splits=splits, tile_keys=tile_keys)
