@@ -61,7 +61,7 @@ def _kernels(width: int, cases, pk: dict) -> dict:
         per = tokens // entries
         step = SimpleNamespace(token_seq=torch.arange(tokens, device=dev, dtype=torch.int32) // per,
                                cu_q=torch.arange(entries + 1, device=dev, dtype=torch.int32) * per,
-                               seq_rows=torch.arange(entries, device=dev, dtype=torch.int32), num_seqs=entries,
+                               seq_rows=torch.arange(entries, device=dev, dtype=torch.int32), num_seqs=entries, max_q_len=per,
                                positions=(torch.arange(tokens, device=dev, dtype=torch.int32) % per) + held)
         kv_len = torch.full((entries,), held + per, device=dev, dtype=torch.int32)
         rec = {}

@@ -129,9 +129,8 @@ retention_scan_kernel(const float* __restrict__ q32, const float* __restrict__ k
 //
 // which is three small matrix products per chunk instead of a chain of n dependent steps.  All of it
 // is 32-bit FMA arithmetic (scores, decays and state enter the recurrence in 32-bit).  One block per
-// (entry, head, 32 value columns): q and k of the chunk lie transposed in shared memory (`[dim][token]`,
-// groups of four tokens XOR-swizzled by the dim so that both the transposing store and the 16-byte
-// reads spread over the banks), the block's slice of the state stays in shared memory over all chunks.
+// (entry, head, 32 value columns): q and k of the chunk lie transposed in shared memory (`[dim][token]`, padded
+// rows), the block's slice of the state stays in shared memory over all chunks.
 constexpr int kChunk = 64;
 constexpr int kChunkThreads = 256;
 
@@ -140,36 +139,46 @@ __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-__device__ __forceinline__ int swz(int i, int t) { return i * kChunk + ((((t >> 2) ^ (i & 15)) << 2) | (t & 3)); }
+// q and k of a chunk lie transposed, `[dim][token]`, rows padded to 68 floats: 16-byte reads along the tokens stay
+// aligned, a walk along the dims is one add per step, and the transposing store spreads over 8 banks.
+constexpr int kPitch = kChunk + 4;
+__device__ __forceinline__ int swz(int i, int t) { return i * kPitch + t; }
 
 template <typename T>
-__global__ void __launch_bounds__(kChunkThreads)
+__global__ void __launch_bounds__(kChunkThreads, 2)
 retention_chunk_kernel(const float* __restrict__ q32, const float* __restrict__ k32, const T* proj, int proj_stride,
                        int v_off, const float* __restrict__ decay, float* state, long long state_stride,
                        const int* __restrict__ cu_q, const int* __restrict__ seq_rows, float* __restrict__ o, int heads,
-                       int d, int dv) {
+                       int d, int dv, int max_seg, int seg_len, float* __restrict__ seg_state) {
     extern __shared__ __align__(16) float chunk_smem[];
-    float* qs = chunk_smem;                      // [d][64] swizzled
-    float* ks = qs + d * kChunk;                 // [d][64] swizzled
-    float* vs = ks + d * kChunk;                 // [64][32]
+    float* qs = chunk_smem;                      // [d][kPitch]
+    float* ks = qs + d * kPitch;                 // [d][kPitch]
+    float* vs = ks + d * kPitch;                 // [64][32]
     float* As = vs + kChunk * 32;                // [64 s][64 t]: g^(t-s) q_t . k_s for s <= t, else 0
     float* Ss = As + kChunk * kChunk;            // [d][32]
     float* gp = Ss + d * 32;                     // [65] powers of the decay
-    const int e = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * 32;
+    // With segments (seg_state != nullptr) block x = entry * max_seg + segment walks `seg_len` tokens of its entry from
+    // a zero state and leaves the state it ends with in seg_state; what the true state at the segment's start adds to
+    // the outputs follows in retention_seg_fix_kernel.  Without, it walks the whole entry from the carried state.
+    const int e = blockIdx.x / max_seg, sg = blockIdx.x - e * max_seg;
+    const int h = blockIdx.y, c0 = blockIdx.z * 32;
     const int lane = threadIdx.x & 31, wg = threadIdx.x >> 5;
-    const int t_first = cu_q[e], t_last = cu_q[e + 1];
+    const int t_first = seg_state != nullptr ? cu_q[e] + sg * seg_len : cu_q[e];
+    const int t_last = seg_state != nullptr ? min(cu_q[e + 1], t_first + seg_len) : cu_q[e + 1];
     if (t_last <= t_first) return;
     const double g = (double)decay[h];
     for (int j = threadIdx.x; j <= kChunk; j += kChunkThreads) gp[j] = (float)pow(g, (double)j);
-    float* S = state + (size_t)seq_rows[e] * state_stride + (size_t)h * d * dv;
+    float* S = seg_state != nullptr ? seg_state + (((size_t)e * max_seg + sg) * heads + h) * d * dv
+                                    : state + (size_t)seq_rows[e] * state_stride + (size_t)h * d * dv;
     const bool col_ok = c0 + lane < dv;
-    for (int x = threadIdx.x; x < d * 32; x += kChunkThreads) Ss[x] = (c0 + (x & 31) < dv) ? S[(size_t)(x >> 5) * dv + c0 + (x & 31)] : 0.f;
+    for (int x = threadIdx.x; x < d * 32; x += kChunkThreads)
+        Ss[x] = (seg_state == nullptr && c0 + (x & 31) < dv) ? S[(size_t)(x >> 5) * dv + c0 + (x & 31)] : 0.f;
 
+    const int ld_t0 = threadIdx.x / d, ld_i0 = threadIdx.x % d, ld_dt = kChunkThreads / d, ld_di = kChunkThreads % d;
     for (int tb = t_first; tb < t_last; tb += kChunk) {
         const int n = min(kChunk, t_last - tb);
         __syncthreads();                          // the chunk before is done with q, k, v and A; the state is up to date
-        for (int x = threadIdx.x; x < kChunk * d; x += kChunkThreads) {
-            const int t = x / d, i = x - t * d;
+        for (int x = threadIdx.x, t = ld_t0, i = ld_i0; x < kChunk * d; x += kChunkThreads) {      // (t, i) = (x / d, x % d)
             const size_t at = ((size_t)(tb + t) * heads + h) * d + i;
             if (t < n) {
                 cp_async4(qs + swz(i, t), q32 + at);
@@ -178,6 +187,9 @@ retention_chunk_kernel(const float* __restrict__ q32, const float* __restrict__ 
                 qs[swz(i, t)] = 0.f;
                 ks[swz(i, t)] = 0.f;
             }
+            t += ld_dt;
+            i += ld_di;
+            if (i >= d) { i -= d; ++t; }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         for (int x = threadIdx.x; x < kChunk * 32; x += kChunkThreads) {
@@ -261,6 +273,83 @@ retention_chunk_kernel(const float* __restrict__ q32, const float* __restrict__ 
         if (c0 + (x & 31) < dv) S[(size_t)(x >> 5) * dv + c0 + (x & 31)] = Ss[x];
 }
 
+// The segments of an entry joined: seg_state[e, j] holds what segment j alone leaves; it becomes the state at
+// segment j's start, S_0 = the carried state, S_(j+1) = g^(len_j) S_j + (what segment j leaves), and the last one
+// goes back to the entry's state row.  One thread per state element.
+__global__ void retention_seg_join_kernel(float* __restrict__ seg_state, float* state, long long state_stride,
+                                          const float* __restrict__ decay, const int* __restrict__ cu_q,
+                                          const int* __restrict__ seq_rows, int heads, int d, int dv, int max_seg,
+                                          int seg_len) {
+    const int e = blockIdx.y, h = blockIdx.z;
+    const int n = cu_q[e + 1] - cu_q[e];
+    if (n <= 0) return;
+    const int nseg = (n + seg_len - 1) / seg_len;
+    const double g = (double)decay[h];
+    const float g_full = (float)pow(g, (double)seg_len), g_last = (float)pow(g, (double)(n - (nseg - 1) * seg_len));
+    float* S = state + (size_t)seq_rows[e] * state_stride + (size_t)h * d * dv;
+    for (int x = blockIdx.x * blockDim.x + threadIdx.x; x < d * dv; x += gridDim.x * blockDim.x) {
+        float cur = S[x];
+        for (int j = 0; j < nseg; ++j) {
+            float* p = seg_state + (((size_t)e * max_seg + j) * heads + h) * d * dv + x;
+            const float left = *p;
+            *p = cur;
+            cur = (j == nseg - 1 ? g_last : g_full) * cur + left;
+        }
+        S[x] = cur;
+    }
+}
+
+// o_t += g^(t' + 1) S_start^T q_t for the tokens of a segment (t' counts from the segment's start): what the state at
+// the segment's start adds to outputs that were computed from a zero state.  Same tiles as the chunked kernel.
+__global__ void __launch_bounds__(kChunkThreads, 2)
+retention_seg_fix_kernel(const float* __restrict__ q32, const float* __restrict__ seg_state, const float* __restrict__ decay,
+                         const int* __restrict__ cu_q, float* __restrict__ o, int heads, int d, int dv, int max_seg,
+                         int seg_len) {
+    extern __shared__ __align__(16) float fix_smem[];
+    float* qs = fix_smem;                        // [d][kPitch]
+    float* Ss = qs + d * kPitch;                 // [d][32]
+    float* gp = Ss + d * 32;                     // [seg_len + 1]
+    const int e = blockIdx.x / max_seg, sg = blockIdx.x - e * max_seg;
+    const int h = blockIdx.y, c0 = blockIdx.z * 32;
+    const int lane = threadIdx.x & 31, wg = threadIdx.x >> 5;
+    const int t_first = cu_q[e] + sg * seg_len, t_last = min(cu_q[e + 1], t_first + seg_len);
+    if (t_last <= t_first) return;
+    const double g = (double)decay[h];
+    for (int j = threadIdx.x; j <= seg_len; j += kChunkThreads) gp[j] = (float)pow(g, (double)j);
+    const float* S = seg_state + (((size_t)e * max_seg + sg) * heads + h) * d * dv;
+    for (int x = threadIdx.x; x < d * 32; x += kChunkThreads) Ss[x] = (c0 + (x & 31) < dv) ? S[(size_t)(x >> 5) * dv + c0 + (x & 31)] : 0.f;
+    const bool col_ok = c0 + lane < dv;
+    for (int tb = t_first; tb < t_last; tb += kChunk) {
+        const int n = min(kChunk, t_last - tb);
+        __syncthreads();
+        for (int x = threadIdx.x, t = threadIdx.x / d, i = threadIdx.x % d; x < kChunk * d; x += kChunkThreads) {
+            if (t < n) cp_async4(qs + swz(i, t), q32 + ((size_t)(tb + t) * heads + h) * d + i);
+            else qs[swz(i, t)] = 0.f;
+            t += kChunkThreads / d;
+            i += kChunkThreads % d;
+            if (i >= d) { i -= d; ++t; }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const int tg = wg * 8;
+        float acc2[8] = {};
+#pragma unroll 4
+        for (int i = 0; i < d; ++i) {
+            const float4 q0 = *reinterpret_cast<const float4*>(qs + swz(i, tg));
+            const float4 q1 = *reinterpret_cast<const float4*>(qs + swz(i, tg + 4));
+            const float sv = Ss[i * 32 + lane];
+            acc2[0] += q0.x * sv; acc2[1] += q0.y * sv; acc2[2] += q0.z * sv; acc2[3] += q0.w * sv;
+            acc2[4] += q1.x * sv; acc2[5] += q1.y * sv; acc2[6] += q1.z * sv; acc2[7] += q1.w * sv;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int t = tg + j;
+            if (t < n && col_ok) o[((size_t)(tb + t) * heads + h) * dv + c0 + lane] += gp[tb - t_first + t + 1] * acc2[j];
+        }
+    }
+}
+
 // out[t, h, :] = o[t, h, :] / sqrt(mean(o[t, h, :]^2) + eps) * silu(gate[t, h, :]); a warp per (token, head).
 template <typename T>
 __global__ void retention_out_kernel(const float* __restrict__ o, const T* proj, int proj_stride, int g_off,
@@ -323,19 +412,41 @@ extern "C" int se_retention_chunk_supported(int d) { return d > 0 && d <= 256; }
 
 extern "C" int se_retention_chunk(const float* q32, const float* k32, const void* proj, int proj_stride, int v_off,
                                   const float* decay, float* state, long long state_stride, const int* cu_q,
-                                  const int* seq_rows, float* o, int entries, int heads, int d, int dv, int dtype,
-                                  cudaStream_t stream) {
+                                  const int* seq_rows, float* o, int entries, int heads, int d, int dv, int max_seg,
+                                  int seg_len, float* seg_state, int dtype, cudaStream_t stream) {
+    // max_seg > 1: the entries' tokens in segments of seg_len (a multiple of 64) that run side by side, joined by
+    // the decay's powers (three launches); seg_state: float [entries, max_seg, heads, d, dv].
     if (entries <= 0) return 0;
     if (!se_retention_chunk_supported(d) || dv <= 0 || heads <= 0 || heads > 65535 || (dv + 31) / 32 > 65535)
         return SE_ERR_UNSUPPORTED;
-    dim3 grid(entries, heads, (dv + 31) / 32);
-    const size_t smem = (size_t)(2 * d * se::kChunk + se::kChunk * 32 + se::kChunk * se::kChunk + d * 32 + se::kChunk + 4) * sizeof(float);
+    if (max_seg < 1 || (max_seg > 1 && (seg_state == nullptr || seg_len <= 0 || seg_len % se::kChunk || seg_len > 8192)))
+        return SE_ERR_ARGUMENT;
+    if ((long long)entries * max_seg > 0x7fffffffLL || entries > 65535) return SE_ERR_UNSUPPORTED;
+    const bool segments = max_seg > 1;
+    dim3 grid(entries * max_seg, heads, (dv + 31) / 32);
+    const size_t smem = (size_t)(2 * d * se::kPitch + se::kChunk * 32 + se::kChunk * se::kChunk + d * 32 + se::kChunk + 4) * sizeof(float);
     SE_DISPATCH_DTYPE(dtype, T, {
         cudaError_t e = cudaFuncSetAttribute(se::retention_chunk_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        // the largest shared-memory carve-out, so that two blocks share an SM where their tiles allow it
+        e = cudaFuncSetAttribute(se::retention_chunk_kernel<T>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        if (e != cudaSuccess) return (int)e;
         se::retention_chunk_kernel<T><<<grid, se::kChunkThreads, smem, stream>>>(
-            q32, k32, (const T*)proj, proj_stride, v_off, decay, state, state_stride, cu_q, seq_rows, o, heads, d, dv);
+            q32, k32, (const T*)proj, proj_stride, v_off, decay, state, state_stride, cu_q, seq_rows, o, heads, d, dv,
+            max_seg, segments ? seg_len : 0, segments ? seg_state : nullptr);
     });
+    if (segments) {
+        const int per = d * dv;
+        se::retention_seg_join_kernel<<<dim3((per + 255) / 256 < 64 ? (per + 255) / 256 : 64, entries, heads), 256, 0, stream>>>(
+            seg_state, state, state_stride, decay, cu_q, seq_rows, heads, d, dv, max_seg, seg_len);
+        const size_t fix_smem = (size_t)(d * se::kPitch + d * 32 + seg_len + 4) * sizeof(float);
+        cudaError_t e = cudaFuncSetAttribute(se::retention_seg_fix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fix_smem);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(se::retention_seg_fix_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+        if (e != cudaSuccess) return (int)e;
+        se::retention_seg_fix_kernel<<<grid, se::kChunkThreads, fix_smem, stream>>>(q32, seg_state, decay, cu_q, o, heads, d, dv,
+                                                                                  max_seg, seg_len);
+    }
     SE_LAUNCH_CHECK();
 }
 

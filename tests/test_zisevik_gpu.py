@@ -451,7 +451,7 @@ def test_chunked_retention_against_the_walk_token_by_token(heads, d, dv, rot):
     cu = [0]
     for n in q_lens:
         cu.append(cu[-1] + n)
-    step = SimpleNamespace(cu_q=torch.tensor(cu, dtype=torch.int32, device=dev), num_seqs=entries,
+    step = SimpleNamespace(cu_q=torch.tensor(cu, dtype=torch.int32, device=dev), num_seqs=entries, max_q_len=max(q_lens),
                            seq_rows=torch.tensor([2, 0, 4, 1, 3], dtype=torch.int32, device=dev))
     positions = torch.cat([torch.arange(500, 500 + n) for n in q_lens]).to(torch.int32).to(dev)
     qk, vv = heads * d, heads * dv
@@ -463,12 +463,15 @@ def test_chunked_retention_against_the_walk_token_by_token(heads, d, dv, rot):
         decay = torch.tensor(([1.0, 0.9995, 0.5, 0.97] * heads)[:heads], dtype=torch.float32, device=dev)
         state0 = torch.randn(5, heads * d * dv, generator=g, device=dev)
         outs = []
-        for fn in (ops.retention_scan, ops.retention_chunk):
+        # the walk token by token; the chunks in one pass; the chunks in segments of 64 and of 128 tokens side by side
+        for fn, kw in ((ops.retention_scan, {}), (ops.retention_chunk, {"segments": (1, 0)}),
+                       (ops.retention_chunk, {"segments": (4, 64)}), (ops.retention_chunk, {"segments": (2, 128)})):
             state = state0.clone()
             o = torch.full((tokens, vv), float("nan"), device=dev)
-            fn(q32, k32, proj, 2 * qk, decay, state, step, o, heads=heads, head_dim=d, v_head_dim=dv)
+            fn(q32, k32, proj, 2 * qk, decay, state, step, o, heads=heads, head_dim=d, v_head_dim=dv, **kw)
             outs.append((o, state))
-        (o1, s1), (o2, s2) = outs
-        assert bool(torch.isfinite(o2).all())
-        assert float((o1 - o2).abs().max()) < 2e-5 * float(o1.abs().max())
-        assert float((s1 - s2).abs().max()) < 2e-5 * float(s1.abs().max())
+        (o1, s1) = outs[0]
+        for o2, s2 in outs[1:]:
+            assert bool(torch.isfinite(o2).all())
+            assert float((o1 - o2).abs().max()) < 2e-5 * float(o1.abs().max())
+            assert float((s1 - s2).abs().max()) < 2e-5 * float(s1.abs().max())
